@@ -26,10 +26,12 @@ def architectures() -> list[str]:
 
 def architecture_of(config_json: dict) -> str:
     names = config_json.get("architectures")
+    if not names and isinstance(config_json.get("architecture"), str):
+        names = [config_json["architecture"]]           # some designs name themselves under a key of their own
     if not names:
         by_type = _BY_MODEL_TYPE.get(config_json.get("model_type"))
         if by_type is None:
-            raise ConfigError("config.json names no known architecture (keys 'architectures', 'model_type')")
+            raise ConfigError("config.json names no known architecture (keys 'architectures', 'architecture', 'model_type')")
         names = [by_type]
     if names[0] not in _ARCHITECTURES:
         raise ConfigError(f"architecture {names[0]!r} is not registered; known: {', '.join(architectures()) or 'none'}")

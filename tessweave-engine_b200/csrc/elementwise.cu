@@ -10,15 +10,15 @@
 namespace cg = cooperative_groups;
 
 // ---------------------------------------------------------------------------
-// Embedding: resid[n, :] = float(table[ids[n], :]).  No scaling
-// (reference: flow_engine/model.py:176).  An id below zero names a token that is still on the
+// Embedding: resid[n, :] = float(table[ids[n], :]) * scale (fp32 product; scale 1 for the reference's
+// model, flow_engine/model.py:176).  An id below zero names a token that is still on the
 // device: -(i + 1) stands for device_tokens[i], the i-th token the previous step sampled, so a
 // step can be launched before the host has seen its input tokens.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ table,
                              const int* __restrict__ ids, const int* __restrict__ device_tokens, int n_device_tokens,
-                             int hidden, int vocab, int* status) {
+                             int hidden, int vocab, float scale, int* status) {
     TW_TIMELINE_SCOPE(TW_K_EMBED);
     tw_grid_wait();
     TW_TIMELINE_MARK();
@@ -41,23 +41,23 @@ __global__ void embed_kernel(float* __restrict__ resid, const T* __restrict__ ta
                 const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
                 const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]);
                 const float2 c = __bfloat1622float2(h2[2]), d = __bfloat1622float2(h2[3]);
-                reinterpret_cast<float4*>(dst)[2 * i] = make_float4(a.x, a.y, b.x, b.y);
-                reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+                reinterpret_cast<float4*>(dst)[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+                reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
             }
             return;
         }
     }
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = tw_to_float(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = tw_to_float(row[i]) * scale;
 }
 
 TW_EXPORT int tw_embed(void* resid, const void* table, const int* ids, const int* device_tokens, int n_device_tokens,
-                       int n_tokens, int hidden, int vocab, int dtype, int* status, cudaStream_t stream) {
+                       int n_tokens, int hidden, int vocab, float scale, int dtype, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dtype == TW_F32)
-        tw_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, 1, (float*)resid, (const float*)table, ids, device_tokens, n_device_tokens, hidden, vocab, status);
+        tw_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, 1, (float*)resid, (const float*)table, ids, device_tokens, n_device_tokens, hidden, vocab, scale, status);
     else
         tw_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, 1, (float*)resid, (const __nv_bfloat16*)table, ids,
-                                                                   device_tokens, n_device_tokens, hidden, vocab, status);
+                                                                   device_tokens, n_device_tokens, hidden, vocab, scale, status);
     return TW_LAUNCH_CHECK();
 }
 
@@ -345,6 +345,166 @@ TW_EXPORT int tw_add_rmsnorm(void* out, float* resid, const void* delta, const f
 }
 
 // ---------------------------------------------------------------------------
+// RMSNorm of a sub-layer's OUTPUT, added to the residual stream (a block that normalises what a
+// sub-layer returns instead of what it reads):
+//   y = delta[r]                            (a tensor of the activation type, or fp32 slices added in slice order)
+//   resid[r] += (y * (1 / sqrt(mean(y^2) + eps))) * weight          all in fp32
+//   copy[r] = T(resid[r])                   (copy may be null: the rows the next sub-layer reads, in its type)
+// ---------------------------------------------------------------------------
+template <typename T, bool ONE_PASS>
+__global__ void __launch_bounds__(TW_NORM_THREADS)
+rmsnorm_to_residual_kernel(float* __restrict__ resid, T* __restrict__ copy, const T* __restrict__ delta,
+                           const float* __restrict__ partial, int nsplit, size_t split_stride,
+                           const float* __restrict__ weight, float eps, int hidden) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    TW_TIMELINE_SCOPE(TW_K_NORM);
+    tw_grid_wait();
+    TW_TIMELINE_MARK();
+    tw_grid_launch_dependents();
+    float* x = resid + (size_t)r * hidden;
+    const T* d = delta ? delta + (size_t)r * hidden : nullptr;
+    const float* ps = partial ? partial + (size_t)r * hidden : nullptr;
+    auto delta_at = [&](int i) -> float {
+        if (d) return tw_to_float(d[i]);
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;      // the order every consumer of a split product uses
+        int k = 0;
+        for (; k + 4 <= nsplit; k += 4) {
+            s0 += ps[(size_t)k * split_stride + i];
+            s1 += ps[(size_t)(k + 1) * split_stride + i];
+            s2 += ps[(size_t)(k + 2) * split_stride + i];
+            s3 += ps[(size_t)(k + 3) * split_stride + i];
+        }
+        for (; k < nsplit; ++k) s0 += ps[(size_t)k * split_stride + i];
+        return (s0 + s1) + (s2 + s3);
+    };
+    T* c = copy ? copy + (size_t)r * hidden : nullptr;
+    if (ONE_PASS) {
+        float v[TW_NORM_MAXV];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < TW_NORM_MAXV; ++j) {
+            const int i = threadIdx.x + j * TW_NORM_THREADS;
+            v[j] = i < hidden ? delta_at(i) : 0.f;
+            ss += v[j] * v[j];
+        }
+        ss = tw_block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+        for (int j = 0; j < TW_NORM_MAXV; ++j) {
+            const int i = threadIdx.x + j * TW_NORM_THREADS;
+            if (i < hidden) {
+                const float nv = x[i] + (v[j] * inv) * weight[i];
+                x[i] = nv;
+                if (c) c[i] = tw_from_float<T>(nv);
+            }
+        }
+    } else {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = delta_at(i);
+            ss += v * v;
+        }
+        ss = tw_block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float nv = x[i] + (delta_at(i) * inv) * weight[i];
+            x[i] = nv;
+            if (c) c[i] = tw_from_float<T>(nv);
+        }
+    }
+}
+
+// The same with four values per access (dense delta, width a multiple of 4 and at most 4 * 256 * V4).
+template <typename T, int V4>
+__global__ void __launch_bounds__(256)
+rmsnorm_to_residual_vec4_kernel(float* __restrict__ resid, T* __restrict__ copy, const T* __restrict__ delta,
+                                const float* __restrict__ weight, float eps, int hidden) {
+    __shared__ float scratch[33];
+    TW_TIMELINE_SCOPE(TW_K_NORM);
+    tw_grid_wait();
+    TW_TIMELINE_MARK();
+    tw_grid_launch_dependents();
+    const int r = blockIdx.x;
+    float4* x4 = reinterpret_cast<float4*>(resid + (size_t)r * hidden);
+    const int n4 = hidden >> 2;
+    float4 v[V4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < V4; ++j) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+            v[j] = tw_load4(delta + (size_t)r * hidden + 4 * i);
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+    }
+    ss = tw_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+#pragma unroll
+    for (int j = 0; j < V4; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 w = w4[i];
+            float4 x = x4[i];
+            x.x += (v[j].x * inv) * w.x; x.y += (v[j].y * inv) * w.y; x.z += (v[j].z * inv) * w.z; x.w += (v[j].w * inv) * w.w;
+            x4[i] = x;
+            if (copy) tw_store4(copy + (size_t)r * hidden + 4 * i, x);
+        }
+    }
+}
+
+template <typename T>
+static int launch_rmsnorm_to_residual(float* resid, T* copy, const T* delta, const float* partial, int nsplit,
+                                      size_t split_stride, const float* weight, float eps, int n_rows, int hidden,
+                                      cudaStream_t stream) {
+    if (!partial && (hidden & 3) == 0 && hidden <= 4 * 256 * TW_NORM_V4) {
+        if (hidden <= 4 * 256 * 4)
+            return tw_launch(rmsnorm_to_residual_vec4_kernel<T, 4>, dim3(n_rows), dim3(256), 0, stream, 1, resid, copy, delta,
+                             weight, eps, hidden);
+        return tw_launch(rmsnorm_to_residual_vec4_kernel<T, TW_NORM_V4>, dim3(n_rows), dim3(256), 0, stream, 1, resid, copy,
+                         delta, weight, eps, hidden);
+    }
+    if (hidden <= TW_NORM_THREADS * TW_NORM_MAXV)
+        return tw_launch(rmsnorm_to_residual_kernel<T, true>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, resid, copy,
+                         delta, partial, nsplit, split_stride, weight, eps, hidden);
+    return tw_launch(rmsnorm_to_residual_kernel<T, false>, dim3(n_rows), dim3(TW_NORM_THREADS), 0, stream, 1, resid, copy,
+                     delta, partial, nsplit, split_stride, weight, eps, hidden);
+}
+
+TW_EXPORT int tw_rmsnorm_to_residual(float* resid, void* copy, const void* delta, const float* partial, int nsplit,
+                                     long split_stride, const float* weight, float eps, int n_rows, int hidden,
+                                     int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (!delta == !partial) return (int)cudaErrorInvalidValue;      // exactly one source
+    if (dtype == TW_F32)
+        return launch_rmsnorm_to_residual<float>(resid, (float*)copy, (const float*)delta, partial, nsplit,
+                                                 (size_t)split_stride, weight, eps, n_rows, hidden, stream);
+    return launch_rmsnorm_to_residual<__nv_bfloat16>(resid, (__nv_bfloat16*)copy, (const __nv_bfloat16*)delta, partial,
+                                                     nsplit, (size_t)split_stride, weight, eps, n_rows, hidden, stream);
+}
+
+// out[i] = T(resid[i]): the fp32 residual rows in the type the matrix products read.
+template <typename T>
+__global__ void round_rows_kernel(T* __restrict__ out, const float* __restrict__ resid, long total) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] = tw_from_float<T>(resid[i]);
+}
+
+TW_EXPORT int tw_round_rows(void* out, const float* resid, long total, int dtype, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (dtype == TW_F32)
+        return tw_launch(round_rows_kernel<float>, dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, resid, total);
+    return tw_launch(round_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, resid,
+                     total);
+}
+
+// ---------------------------------------------------------------------------
 // Bias + rotary position encoding + cache write, one block per token.
 //
 // qkv row layout: [q heads | k heads | v heads], each head `D` wide.
@@ -555,6 +715,47 @@ TW_EXPORT int tw_rope_kv_write(void* qkv, int qkv_stride, const float* partial, 
             seq_slot, block_table, table_stride, inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,
             status);
     return TW_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// Rotation of pairs in place, on the first `n_heads` heads of each packed row and the first `rot_dims`
+// values of a head: angle = float(position) * inv_freq[i]; pair i is (2i, 2i+1) when `interleaved`, else
+// (i, i + rot_dims / 2).  The general form of the rotation above, for encodings no fused kernel takes.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rotate_pairs_kernel(T* __restrict__ rows, int row_stride, const int* __restrict__ positions,
+                                    const int* __restrict__ seq_of_token, const float* __restrict__ inv_freq, int n_heads,
+                                    int D, int rot_dims, int interleaved) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int n = blockIdx.x;
+    if (seq_of_token[n] < 0) return;
+    const int pos = positions[n];
+    const int half = rot_dims >> 1;
+    T* row = rows + (size_t)n * row_stride;
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < n_heads * half; idx += gridDim.y * blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const int a = head * D + (interleaved ? 2 * i : i), b = head * D + (interleaved ? 2 * i + 1 : i + half);
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        const float u = tw_to_float(row[a]), v = tw_to_float(row[b]);
+        row[a] = tw_from_float<T>(u * cs - v * sn);
+        row[b] = tw_from_float<T>(v * cs + u * sn);
+    }
+}
+
+TW_EXPORT int tw_rotate_pairs(void* rows, int row_stride, const int* positions, const int* seq_of_token,
+                              const float* inv_freq, int n_tokens, int n_heads, int D, int rot_dims, int interleaved,
+                              int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || rot_dims < 2) return 0;
+    if (rot_dims > D || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
+    const int work = n_heads * (rot_dims / 2);
+    const dim3 grid(n_tokens, (work + 127) / 128 < 8 ? (work + 127) / 128 : 8);
+    if (dtype == TW_F32)
+        return tw_launch(rotate_pairs_kernel<float>, grid, dim3(128), 0, stream, 1, (float*)rows, row_stride, positions,
+                         seq_of_token, inv_freq, n_heads, D, rot_dims, interleaved);
+    return tw_launch(rotate_pairs_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, (__nv_bfloat16*)rows, row_stride,
+                     positions, seq_of_token, inv_freq, n_heads, D, rot_dims, interleaved);
 }
 
 // ---------------------------------------------------------------------------

@@ -98,8 +98,8 @@ def _fn(lib_name: str, fn_name: str, defines=None):
 
 # ---------------------------------------------------------------------------
 def embed(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens: int, status: torch.Tensor,
-          device_tokens: torch.Tensor | None = None) -> None:
-    """resid[n] = float(table[ids[n]]); resid is fp32 [>=n_tokens, hidden].  An id -(i + 1) is
+          device_tokens: torch.Tensor | None = None, scale: float = 1.0) -> None:
+    """resid[n] = float(table[ids[n]]) * scale; resid is fp32 [>=n_tokens, hidden].  An id -(i + 1) is
     replaced by ``device_tokens[i]`` (int32, on the device) inside the kernel."""
     _cuda(resid, table, ids, status, device_tokens)
     _need(device_tokens is None or device_tokens.dtype == torch.int32, "embed: device tokens must be int32")
@@ -109,9 +109,130 @@ def embed(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens:
           "embed: shapes disagree")
     code = _fn("elementwise", "tw_embed")(_ptr(resid), _ptr(table), _ptr(ids), _ptr(device_tokens),
                                           c_int(0 if device_tokens is None else device_tokens.numel()), c_int(n_tokens),
-                                          c_int(table.shape[1]), c_int(table.shape[0]),
+                                          c_int(table.shape[1]), c_int(table.shape[0]), c_float(scale),
                                           c_int(dtype_code(table.dtype)), _ptr(status), _stream())
     _check(code, "embed")
+
+
+def rmsnorm_to_residual(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, n_rows: int,
+                        copy: torch.Tensor | None = None) -> None:
+    """resid += rmsnorm(delta) * weight (in place, fp32 statistics and sum); ``copy`` (may be None) receives the
+    new rows in its own type, for the product that reads them next.  ``delta`` is a tensor of the
+    activation type (the type of ``copy``; fp32 where there is no copy) or a ``SplitSum``."""
+    partial, nsplit, split_stride = None, 0, 0
+    hidden = resid.shape[1]
+    if isinstance(delta, SplitSum):
+        partial, nsplit, split_stride = delta.slices, delta.slices.shape[0], delta.slices.stride(0)
+        _need(partial.dtype == torch.float32 and partial.shape[2] == hidden and partial[0].is_contiguous()
+              and partial.shape[1] >= n_rows, "rmsnorm_to_residual: split sum must be fp32 [slices, rows, hidden]")
+        delta = None
+    _cuda(resid, delta, weight, copy, partial)
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape[0] >= n_rows,
+          "rmsnorm_to_residual: residual stream must be contiguous fp32")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden, "rmsnorm_to_residual: weight must be fp32 [hidden]")
+    dtype = copy.dtype if copy is not None else (delta.dtype if delta is not None else torch.float32)
+    if copy is not None:
+        _need(copy.is_contiguous() and copy.shape[1] == hidden and copy.shape[0] >= n_rows, "rmsnorm_to_residual: bad copy")
+    if delta is not None:
+        _need(delta.dtype == dtype and delta.is_contiguous() and delta.shape[1] == hidden and delta.shape[0] >= n_rows,
+              "rmsnorm_to_residual: delta must be contiguous [rows, hidden] of the activation type")
+    code = _fn("elementwise", "tw_rmsnorm_to_residual")(_ptr(resid), _ptr(copy), _ptr(delta), _ptr(partial), c_int(nsplit),
+                                                        c_long(split_stride), _ptr(weight), c_float(eps), c_int(n_rows),
+                                                        c_int(hidden), c_int(dtype_code(dtype)), _stream())
+    _check(code, "rmsnorm_to_residual")
+
+
+def round_rows(out: torch.Tensor, resid: torch.Tensor, n_rows: int) -> None:
+    """out[:n_rows] = resid[:n_rows] in the type of ``out``."""
+    _cuda(out, resid)
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous()
+          and out.shape[1] == resid.shape[1] and min(out.shape[0], resid.shape[0]) >= n_rows, "round_rows: bad operands")
+    code = _fn("elementwise", "tw_round_rows")(_ptr(out), _ptr(resid), c_long(n_rows * resid.shape[1]),
+                                               c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "round_rows")
+
+
+# ---------------------------------------------------------------------------
+# sigmoid attention with mixed heads (csrc/sigmoid_attention.cu)
+# ---------------------------------------------------------------------------
+def sigmoid_attention_prepare(qf: torch.Tensor, proj: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torch.Tensor,
+                              eps: float, mix: torch.Tensor | None, scale: float, inv_freq: torch.Tensor | None,
+                              rot_dims: int, interleaved: bool, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                              seq_slot: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                              v_pages: torch.Tensor, n_tokens: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                              write_cache: bool, status: torch.Tensor) -> None:
+    """Per token: norms over the whole q and k projections, rotation, the raw key into the value pages, the
+    normalised rotated key into the key pages, the folded query ``qf`` [rows, Hq, Hkv * D] (the heads' mixing
+    matrix ``mix`` [Hq, Hq] and ``scale`` applied).  ``proj`` rows are [q | k | anything]."""
+    _cuda(qf, proj, q_norm_w, k_norm_w, mix, inv_freq, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status)
+    qw, kw = n_q_heads * head_dim, n_kv_heads * head_dim
+    _need(proj.stride(1) == 1 and proj.shape[1] >= qw + kw and proj.shape[0] >= n_tokens, "sigmoid attention: bad projection rows")
+    _need(qf.is_contiguous() and qf.dtype == proj.dtype and qf.numel() >= n_tokens * n_q_heads * kw,
+          "sigmoid attention: folded queries must be contiguous [rows, Hq, Hkv * D] of the activation type")
+    _need(q_norm_w.dtype == torch.float32 and q_norm_w.numel() == qw and k_norm_w.dtype == torch.float32
+          and k_norm_w.numel() == kw, "sigmoid attention: norm weights must be fp32 [Hq * D] and [Hkv * D]")
+    if mix is not None:
+        _need(mix.dtype == torch.float32 and mix.is_contiguous() and tuple(mix.shape) == (n_q_heads, n_q_heads),
+              "sigmoid attention: the mixing matrix must be fp32 [Hq, Hq]")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2 and rot_dims % 2 == 0
+              and rot_dims <= head_dim, "sigmoid attention: inv_freq must be fp32 [rot_dims / 2], rot_dims even and <= D")
+    _need(k_pages.dtype == proj.dtype and v_pages.dtype == proj.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
+          and tuple(k_pages.shape[1:]) == (n_kv_heads, k_pages.shape[2], head_dim) and v_pages.shape == k_pages.shape,
+          "sigmoid attention: cache pages must be contiguous [pages, kv_heads, page, head_dim] of the activation type")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(),
+          "sigmoid attention: block table must be contiguous int32 [requests, blocks]")
+    code = _fn("sigmoid_attention", "tw_sigattn_prepare")(
+        _ptr(proj), c_int(proj.stride(0)), _ptr(q_norm_w), _ptr(k_norm_w), c_float(eps), _ptr(mix), c_float(scale),
+        _ptr(inv_freq), c_int(rot_dims if inv_freq is not None else 0), c_int(1 if interleaved else 0), _ptr(positions),
+        _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(qf), _ptr(k_pages),
+        _ptr(v_pages), c_int(n_tokens), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(k_pages.shape[2]),
+        c_int(k_pages.shape[0]), c_int(1 if write_cache else 0), c_int(dtype_code(proj.dtype)), _ptr(status), _stream())
+    _check(code, "sigmoid_attention_prepare")
+
+
+def sigmoid_attention_generic(out: torch.Tensor, qf: torch.Tensor, bias: torch.Tensor | None, gate: torch.Tensor | None,
+                              positions: torch.Tensor, seq_of_token: torch.Tensor, seq_slot: torch.Tensor,
+                              block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, n_tokens: int,
+                              n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, status: torch.Tensor) -> None:
+    """Exact paged causal sigmoid attention, one block per (token, head): out[n, h] = sum over visible keys of
+    sigmoid(qf[n, h] . k + bias[h]) * v, then * sigmoid(gate[n, h]) where a gate is given (a column slice of
+    the projection buffer is fine: its row stride is passed on)."""
+    _cuda(out, qf, bias, gate, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status)
+    _need(head_dim <= 256 and n_q_heads % n_kv_heads == 0, "sigmoid attention: head_dim above 256 or bad head counts")
+    _need(out.stride(1) == 1 and qf.is_contiguous() and qf.dtype == out.dtype == k_pages.dtype, "sigmoid attention: bad operands")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == n_q_heads), "sigmoid attention: bias must be fp32 [Hq]")
+    _need(gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1 and gate.shape[1] >= n_q_heads * head_dim),
+          "sigmoid attention: gate must be [rows, Hq * D] of the activation type")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "sigmoid attention: bad block table")
+    code = _fn("sigmoid_attention", "tw_sigattn_generic")(
+        _ptr(out), c_int(out.stride(0)), _ptr(qf), _ptr(bias), _ptr(gate), c_int(0 if gate is None else gate.stride(0)),
+        _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages),
+        _ptr(v_pages), c_int(n_tokens), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(k_pages.shape[2]),
+        c_int(k_pages.shape[0]), c_int(window), c_int(dtype_code(out.dtype)), _ptr(status), _stream())
+    _check(code, "sigmoid_attention_generic")
+
+
+# ---------------------------------------------------------------------------
+# gated recurrences with a fixed-size state per request (csrc/recurrent.cu)
+# ---------------------------------------------------------------------------
+def mingru_scan(out: torch.Tensor, proj: torch.Tensor, bias_z: torch.Tensor | None, bias_x: torch.Tensor | None,
+                state: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor,
+                n_seqs: int, width: int, write_state: bool = True) -> None:
+    """Rows of ``proj`` are [z | x | g] pre-activations (each ``width`` wide); for every request of the step the
+    state S (fp32 [slots, width], row ``seq_slot``) runs through its rows: S = (1 - z) S + z c, and
+    out = S * silu(g) in the type of ``out``."""
+    _cuda(out, proj, bias_z, bias_x, state, seq_slot, seq_q_start, seq_q_len)
+    _need(proj.stride(1) == 1 and proj.shape[1] >= 3 * width and out.stride(1) == 1 and out.shape[1] >= width
+          and out.dtype == proj.dtype, "mingru: rows must be [z | x | g] and the output of the same type")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width, "mingru: state must be fp32 [slots, width]")
+    for b in (bias_z, bias_x):
+        _need(b is None or (b.dtype == torch.float32 and b.numel() == width), "mingru: biases must be fp32 [width]")
+    code = _fn("recurrent", "tw_mingru_scan")(
+        _ptr(out), c_int(out.stride(0)), _ptr(proj), c_int(proj.stride(0)), _ptr(bias_z), _ptr(bias_x), _ptr(state),
+        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(width), c_int(1 if write_state else 0),
+        c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "mingru_scan")
 
 
 def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor,
@@ -202,6 +323,21 @@ def rotate_heads(rows: torch.Tensor, bias: torch.Tensor | None, positions: torch
         c_int(0), _ptr(inv_freq), _ptr(None), _ptr(None), c_int(n_tokens), c_int(n_heads), c_int(0), c_int(head_dim),
         c_int(1), c_int(0), c_int(0), c_int(dtype_code(rows.dtype)), _ptr(None), _stream())
     _check(code, "rotate_heads")
+
+
+def rotate_pairs(rows: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, inv_freq: torch.Tensor,
+                 n_tokens: int, n_heads: int, head_dim: int, rot_dims: int, interleaved: bool) -> None:
+    """In place on the first ``n_heads`` heads of each packed row: rotate ``rot_dims / 2`` pairs at the start of
+    every head by ``position * inv_freq[i]``; pair i is (2i, 2i+1) when ``interleaved``, else (i, i + rot_dims / 2)."""
+    _cuda(rows, positions, seq_of_token, inv_freq)
+    _need(rows.stride(1) == 1 and rows.shape[1] >= n_heads * head_dim, "rotate_pairs: bad rows")
+    _need(rot_dims % 2 == 0 and 0 <= rot_dims <= head_dim and inv_freq.dtype == torch.float32
+          and inv_freq.numel() == rot_dims // 2, "rotate_pairs: inv_freq must be fp32 [rot_dims / 2], rot_dims even and <= D")
+    code = _fn("elementwise", "tw_rotate_pairs")(_ptr(rows), c_int(rows.stride(0)), _ptr(positions), _ptr(seq_of_token),
+                                                 _ptr(inv_freq), c_int(n_tokens), c_int(n_heads), c_int(head_dim),
+                                                 c_int(rot_dims), c_int(1 if interleaved else 0),
+                                                 c_int(dtype_code(rows.dtype)), _stream())
+    _check(code, "rotate_pairs")
 
 
 def silu_mul(out: torch.Tensor, gate_up, n_rows: int, interleaved: bool = False) -> None:

@@ -1,0 +1,58 @@
+// Gated linear recurrences with a state of fixed size per request.
+//
+// minGRU: the gates read only the current token, so a request's rows form the first-order recurrence
+//   z_t = sigmoid(pz_t + bz)         u_t = px_t + bx        c_t = u_t + 1/2 (u_t >= 0), sigmoid(u_t) (u_t < 0)
+//   S_t = (1 - z_t) S_{t-1} + z_t c_t                        element by element, fp32, S_{-1} = the request's state
+//   out_t = T(S_t * silu(pg_t))
+// with pz | px | pg the three column blocks of one projection row.  The state slot of a request is read at
+// the first row of a step and written back after its last, so a request may be cut into steps anywhere.
+// Everything behind the projection is fp32.
+#include "common.cuh"
+
+#define TW_SCAN_THREADS 128
+
+__device__ __forceinline__ float tw_sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// One thread per (request, channel) walks the request's rows of this step in order.
+template <typename T>
+__global__ void __launch_bounds__(TW_SCAN_THREADS)
+mingru_scan_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ proj, int proj_stride,
+                   const float* __restrict__ bias_z, const float* __restrict__ bias_x, float* __restrict__ state,
+                   const int* __restrict__ seq_slot, const int* __restrict__ seq_q_start,
+                   const int* __restrict__ seq_q_len, int width, int write_state) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int s = blockIdx.y;
+    const int ch = blockIdx.x * TW_SCAN_THREADS + threadIdx.x;
+    const int len = seq_q_len[s];
+    if (ch >= width || len <= 0) return;
+    const int start = seq_q_start[s];
+    float* slot = state + (size_t)seq_slot[s] * width;
+    float S = slot[ch];
+    const float bz = bias_z ? bias_z[ch] : 0.f, bx = bias_x ? bias_x[ch] : 0.f;
+    for (int t = 0; t < len; ++t) {
+        const T* row = proj + (size_t)(start + t) * proj_stride;
+        const float z = tw_sigmoidf(tw_to_float(row[ch]) + bz);
+        const float u = tw_to_float(row[width + ch]) + bx;
+        const float g = tw_to_float(row[2 * width + ch]);
+        const float c = u >= 0.f ? u + 0.5f : tw_sigmoidf(u);
+        S = (1.0f - z) * S + z * c;
+        out[(size_t)(start + t) * out_stride + ch] = tw_from_float<T>(S * (g * tw_sigmoidf(g)));
+    }
+    if (write_state) slot[ch] = S;
+}
+
+TW_EXPORT int tw_mingru_scan(void* out, int out_stride, const void* proj, int proj_stride, const float* bias_z,
+                             const float* bias_x, float* state, const int* seq_slot, const int* seq_q_start,
+                             const int* seq_q_len, int n_seqs, int width, int write_state, int dtype,
+                             cudaStream_t stream) {
+    if (n_seqs <= 0 || width <= 0) return 0;
+    const dim3 grid((width + TW_SCAN_THREADS - 1) / TW_SCAN_THREADS, n_seqs);
+    if (dtype == TW_F32)
+        return tw_launch(mingru_scan_kernel<float>, grid, dim3(TW_SCAN_THREADS), 0, stream, 1, (float*)out, out_stride,
+                         (const float*)proj, proj_stride, bias_z, bias_x, state, seq_slot, seq_q_start, seq_q_len, width,
+                         write_state);
+    return tw_launch(mingru_scan_kernel<__nv_bfloat16>, grid, dim3(TW_SCAN_THREADS), 0, stream, 1, (__nv_bfloat16*)out,
+                     out_stride, (const __nv_bfloat16*)proj, proj_stride, bias_z, bias_x, state, seq_slot, seq_q_start,
+                     seq_q_len, width, write_state);
+}

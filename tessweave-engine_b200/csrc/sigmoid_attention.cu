@@ -1,0 +1,258 @@
+// Sigmoid attention with mixed heads over a paged cache: preparation of queries and keys, and the
+// exact-arithmetic attention kernel (fp32 scores and sums, any sizes, float32 or bfloat16 storage).
+//
+// The mechanism, for a token at position i of a request with H query heads, G key/value heads of size D
+// (query head h reads key/value head c(h) = h / (H / G)):
+//
+//   q = rms(Wq x) * nq, k = rms(Wk x) * nk       each norm over the WHOLE projection (all heads at once)
+//   v = Wk x                                      the values are the keys as projected: no norm, no rotation
+//   q, k rotated by position on the first R dims of every head
+//   s_g(i, j)  = scale * q_g(i) . k_c(g)(j)
+//   s'_h(i, j) = sum_g M[h, g] s_g(i, j)          M: H x H, mixes the heads' scores
+//   w_h(i, j)  = sigmoid(s'_h(i, j) + b_h)        j <= i [and j > i - window]; never normalised over j
+//   o_h(i)     = sum_j w_h(i, j) v_c(h)(j)        then o * sigmoid(gate) where a gate is given
+//
+// The mixing is linear in the queries, so it is done once per token instead of once per (token, key):
+//   s'_h(i, j) = sum_c qf_h,c(i) . k_c(j),   qf_h,c = scale * sum_{g in group c} M[h, g] q_g
+// The "folded" query of head h is the row [qf_h,0 | qf_h,1 | ...] of G * D values and meets the keys of ALL
+// key/value heads of a position; after that every head is an ordinary attention head whose weight is a sigmoid.
+// Without M (null) the fold is scale * q_h in its own group's columns and zero elsewhere.
+#include "common.cuh"
+
+#define TW_SIG_PREP_THREADS 256
+
+// ---------------------------------------------------------------------------------------
+// Preparation, one block per token: norms over the whole projections, rotation, the raw key into the
+// value pages, the normalised rotated key into the key pages, the folded query into `qf`.
+//   proj row: [q heads | k heads | ...] (what follows is not touched)
+//   rotation: angle = float(position) * inv_freq[i], i < rot_dims / 2; pair (2i, 2i+1) of a head when
+//   `interleaved`, else (i, i + rot_dims / 2); dims from rot_dims on pass unchanged.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(TW_SIG_PREP_THREADS)
+sigattn_prepare_kernel(const T* __restrict__ proj, int proj_stride, const float* __restrict__ q_norm_w,
+                       const float* __restrict__ k_norm_w, float eps, const float* __restrict__ mix, float scale,
+                       const float* __restrict__ inv_freq, int rot_dims, int interleaved,
+                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                       const int* __restrict__ seq_slot, const int* __restrict__ block_table, int table_stride,
+                       T* __restrict__ qf, T* __restrict__ k_cache, T* __restrict__ v_cache, int Hq, int Hkv, int D,
+                       int page_size, int num_pages, int write_cache, int* status) {
+    extern __shared__ float smem[];          // q: Hq * D, k: Hkv * D, then 33 floats for the reductions
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int n = blockIdx.x;
+    const int s = seq_of_token[n];
+    if (s < 0) return;                       // padding row of a fixed-size batch
+    const int pos = positions[n];
+    const int QW = Hq * D, KW = Hkv * D;
+    float* sq = smem;
+    float* sk = smem + QW;
+    float* scratch = sk + KW;
+    const T* row = proj + (size_t)n * proj_stride;
+
+    int page = -1;
+    if (write_cache) {
+        const int blk = pos / page_size;
+        page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(status, TW_ERR_PAGE);
+            page = -1;
+        }
+    }
+    const int in_page = pos % page_size;
+
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = threadIdx.x; i < QW; i += blockDim.x) {
+        const float v = tw_to_float(row[i]);
+        sq[i] = v;
+        ssq += v * v;
+    }
+    for (int i = threadIdx.x; i < KW; i += blockDim.x) {
+        const T raw = row[QW + i];
+        const float v = tw_to_float(raw);
+        sk[i] = v;
+        ssk += v * v;
+        if (page >= 0) {                     // the value is the key as projected
+            const int c = i / D, d = i - c * D;
+            v_cache[(((size_t)page * Hkv + c) * page_size + in_page) * D + d] = raw;
+        }
+    }
+    ssq = tw_block_sum(ssq, scratch);
+    ssk = tw_block_sum(ssk, scratch);
+    const float inv_q = 1.0f / sqrtf(ssq / (float)QW + eps);
+    const float inv_k = 1.0f / sqrtf(ssk / (float)KW + eps);
+    for (int i = threadIdx.x; i < QW; i += blockDim.x) sq[i] = (sq[i] * inv_q) * q_norm_w[i];
+    for (int i = threadIdx.x; i < KW; i += blockDim.x) sk[i] = (sk[i] * inv_k) * k_norm_w[i];
+    __syncthreads();
+    if (inv_freq && rot_dims > 1) {
+        const int half = rot_dims >> 1;
+        const int pairs = (Hq + Hkv) * half;
+        for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
+            const int head = idx / half, i = idx - head * half;
+            float* base = (head < Hq ? sq + head * D : sk + (head - Hq) * D);
+            const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float u = base[a], v = base[b];
+            base[a] = u * cs - v * sn;
+            base[b] = v * cs + u * sn;
+        }
+        __syncthreads();
+    }
+    if (page >= 0) {
+        for (int i = threadIdx.x; i < KW; i += blockDim.x) {
+            const int c = i / D, d = i - c * D;
+            k_cache[(((size_t)page * Hkv + c) * page_size + in_page) * D + d] = tw_from_float<T>(sk[i]);
+        }
+    }
+    const int group = Hq / Hkv;
+    T* out = qf + (size_t)n * Hq * KW;
+    for (int idx = threadIdx.x; idx < Hq * KW; idx += blockDim.x) {
+        const int h = idx / KW, rem = idx - h * KW;
+        const int c = rem / D, d = rem - c * D;
+        float acc = 0.f;
+        if (mix) {
+            for (int g = c * group; g < (c + 1) * group; ++g) acc += mix[h * Hq + g] * sq[g * D + d];
+        } else if (h / group == c) {
+            acc = sq[h * D + d];
+        }
+        out[idx] = tw_from_float<T>(acc * scale);
+    }
+}
+
+TW_EXPORT int tw_sigattn_prepare(const void* proj, int proj_stride, const float* q_norm_w, const float* k_norm_w,
+                                 float eps, const float* mix, float scale, const float* inv_freq, int rot_dims,
+                                 int interleaved, const int* positions, const int* seq_of_token, const int* seq_slot,
+                                 const int* block_table, int table_stride, void* qf, void* k_cache, void* v_cache,
+                                 int n_tokens, int Hq, int Hkv, int D, int page_size, int num_pages, int write_cache,
+                                 int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (D <= 0 || Hkv <= 0 || Hq % Hkv || rot_dims < 0 || rot_dims > D || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
+    const size_t smem = ((size_t)(Hq + Hkv) * D + 33) * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    cudaError_t e;
+    if (dtype == TW_F32) {
+        e = cudaFuncSetAttribute(sigattn_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        return tw_launch(sigattn_prepare_kernel<float>, dim3(n_tokens), dim3(TW_SIG_PREP_THREADS), smem, stream, 1,
+                         (const float*)proj, proj_stride, q_norm_w, k_norm_w, eps, mix, scale, inv_freq, rot_dims,
+                         interleaved, positions, seq_of_token, seq_slot, block_table, table_stride, (float*)qf,
+                         (float*)k_cache, (float*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache, status);
+    }
+    e = cudaFuncSetAttribute(sigattn_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return tw_launch(sigattn_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(TW_SIG_PREP_THREADS), smem, stream, 1,
+                     (const __nv_bfloat16*)proj, proj_stride, q_norm_w, k_norm_w, eps, mix, scale, inv_freq, rot_dims,
+                     interleaved, positions, seq_of_token, seq_slot, block_table, table_stride, (__nv_bfloat16*)qf,
+                     (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,
+                     status);
+}
+
+// ---------------------------------------------------------------------------------------
+// Exact attention, one block per (token, head): the folded query (G * D values, fp32 in shared memory)
+// meets the keys lo..position of its request, key p in warp p % 4, so the order of the sums at a
+// position depends neither on how the request was cut into steps nor on what else is in the batch.
+//   w = 1 / (1 + exp(-(qf . k + bias[head])))        acc += w * v_c(head)
+// gate (may be null): out *= 1 / (1 + exp(-gate[n, head * D + d])).
+// ---------------------------------------------------------------------------------------
+#define TW_SIG_WARPS 4
+#define TW_SIG_MAXR 8       // head_dim <= 32 * 8
+
+template <typename T>
+__global__ void __launch_bounds__(32 * TW_SIG_WARPS)
+sigattn_generic_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ qf, const float* __restrict__ bias,
+                       const T* __restrict__ gate, int gate_stride, const int* __restrict__ positions,
+                       const int* __restrict__ seq_of_token, const int* __restrict__ seq_slot,
+                       const int* __restrict__ block_table, int table_stride, const T* __restrict__ k_cache,
+                       const T* __restrict__ v_cache, int Hq, int Hkv, int D, int page_size, int num_pages, int window,
+                       int* status) {
+    extern __shared__ float smem[];          // folded query: Hkv * D; then TW_SIG_WARPS * D for the merge
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int n = blockIdx.x, head = blockIdx.y;
+    const int s = seq_of_token[n];
+    if (s < 0) return;
+    const int pos = positions[n];
+    const int KW = Hkv * D;
+    const int kvh = head / (Hq / Hkv);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int* table = block_table + (size_t)seq_slot[s] * table_stride;
+    float* sqf = smem;
+    float* merge = smem + KW;
+    const T* qrow = qf + ((size_t)n * Hq + head) * KW;
+    for (int i = threadIdx.x; i < KW; i += blockDim.x) sqf[i] = tw_to_float(qrow[i]);
+    __syncthreads();
+    const float b = bias ? bias[head] : 0.f;
+    float acc[TW_SIG_MAXR];
+#pragma unroll
+    for (int j = 0; j < TW_SIG_MAXR; ++j) acc[j] = 0.f;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int p = lo + ((warp - lo) % TW_SIG_WARPS + TW_SIG_WARPS) % TW_SIG_WARPS;
+    for (; p <= pos; p += TW_SIG_WARPS) {
+        const int blk = p / page_size;
+        const int page = blk < table_stride ? table[blk] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) atomicOr(status, TW_ERR_PAGE);
+            continue;
+        }
+        const int in_page = p - blk * page_size;
+        float dot = 0.f;
+        for (int c = 0; c < Hkv; ++c) {
+            const T* kr = k_cache + (((size_t)page * Hkv + c) * page_size + in_page) * D;
+            const float* qc = sqf + c * D;
+            for (int d = lane; d < D; d += 32) dot += qc[d] * tw_to_float(kr[d]);
+        }
+        dot = tw_warp_sum(dot);
+        const float w = 1.0f / (1.0f + expf(-(dot + b)));
+        const T* vr = v_cache + (((size_t)page * Hkv + kvh) * page_size + in_page) * D;
+#pragma unroll
+        for (int j = 0; j < TW_SIG_MAXR; ++j) {
+            const int d = lane + 32 * j;
+            if (d < D) acc[j] += w * tw_to_float(vr[d]);
+        }
+    }
+    float* my = merge + warp * D;
+#pragma unroll
+    for (int j = 0; j < TW_SIG_MAXR; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) my[d] = acc[j];
+    }
+    __syncthreads();
+    T* orow = out + (size_t)n * out_stride + head * D;
+    const T* grow = gate ? gate + (size_t)n * gate_stride + head * D : nullptr;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < TW_SIG_WARPS; ++w) o += merge[w * D + d];
+        if (grow) o *= 1.0f / (1.0f + expf(-tw_to_float(grow[d])));
+        orow[d] = tw_from_float<T>(o);
+    }
+}
+
+TW_EXPORT int tw_sigattn_generic(void* out, int out_stride, const void* qf, const float* bias, const void* gate,
+                                 int gate_stride, const int* positions, const int* seq_of_token, const int* seq_slot,
+                                 const int* block_table, int table_stride, const void* k_cache, const void* v_cache,
+                                 int n_tokens, int Hq, int Hkv, int D, int page_size, int num_pages, int window,
+                                 int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (D <= 0 || D > 32 * TW_SIG_MAXR || Hkv <= 0 || Hq % Hkv) return (int)cudaErrorInvalidValue;
+    const dim3 grid(n_tokens, Hq);
+    const size_t smem = ((size_t)Hkv * D + (size_t)TW_SIG_WARPS * D) * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    cudaError_t e;
+    if (dtype == TW_F32) {
+        e = cudaFuncSetAttribute(sigattn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        return tw_launch(sigattn_generic_kernel<float>, grid, dim3(32 * TW_SIG_WARPS), smem, stream, 1, (float*)out,
+                         out_stride, (const float*)qf, bias, (const float*)gate, gate_stride, positions, seq_of_token,
+                         seq_slot, block_table, table_stride, (const float*)k_cache, (const float*)v_cache, Hq, Hkv, D,
+                         page_size, num_pages, window, status);
+    }
+    e = cudaFuncSetAttribute(sigattn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return tw_launch(sigattn_generic_kernel<__nv_bfloat16>, grid, dim3(32 * TW_SIG_WARPS), smem, stream, 1,
+                     (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)qf, bias, (const __nv_bfloat16*)gate,
+                     gate_stride, positions, seq_of_token, seq_slot, block_table, table_stride,
+                     (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages,
+                     window, status);
+}

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import FixedState, PagedKV, Runtime, StepContext, WeightDecl, build_part
+from ..parts.base import FixedState, PagedKV, Runtime, StepContext, WeightDecl, build_part, join_name
 from .spec import ModelSpec
 
 
@@ -41,7 +41,7 @@ class Model:
         decls: dict[str, WeightDecl] = {}
         for prefix, part in self.named_parts():
             for w in part.weights():
-                name = f"{prefix}.{w.name}" if prefix else w.name
+                name = join_name(prefix, w.name)
                 if name in decls:
                     raise ValueError(f"two parts declare the weight {name!r}")
                 decls[name] = WeightDecl(name, tuple(w.shape), w.role, w.init, w.dest)
@@ -49,7 +49,7 @@ class Model:
 
     def redundant_names(self) -> set[str]:
         """Checkpoint tensors that are skipped without complaint (see ``Part.redundant_names``)."""
-        return {f"{prefix}.{name}" if prefix else name for prefix, part in self.named_parts()
+        return {join_name(prefix, name) for prefix, part in self.named_parts()
                 for name in part.redundant_names()}
 
     def finalize(self) -> None:

@@ -41,6 +41,12 @@ class PartSpec:
         return PartSpec(self.kind, {**self.params, **more})
 
 
+def join_name(prefix: str, name: str) -> str:
+    """Checkpoint name of ``name`` below ``prefix``; either may be empty (a part whose only tensor
+    carries the part's own name declares it as ``""``)."""
+    return f"{prefix}.{name}" if prefix and name else (prefix or name)
+
+
 @dataclass
 class WeightDecl:
     """One tensor a part expects from the checkpoint.
@@ -272,6 +278,21 @@ class Norm(Part):
                 rows: torch.Tensor | None = None) -> None:
         raise NotImplementedError
 
+    def add_normed(self, ctx: "StepContext", resid: torch.Tensor, delta, n_rows: int,
+                   copy: torch.Tensor | None = None) -> None:
+        """resid += norm(delta), for a block that normalises what a sub-layer returns; ``copy`` (may be None)
+        receives the new rows in the activation type.  ``delta`` as in ``apply``."""
+        raise NotImplementedError(f"norm kind {getattr(self, 'kind', type(self).__name__)!r} cannot normalise into the residual stream")
+
+
+@dataclass(frozen=True)
+class RotaryPlan:
+    """A rotation by ``position * inv_freq[i]`` of ``rot_dims / 2`` pairs at the start of every head: pair i is
+    ``(2i, 2i + 1)`` when ``interleaved``, else ``(i, i + rot_dims / 2)``; dims from ``rot_dims`` on pass unchanged."""
+    inv_freq: torch.Tensor          # fp32 [rot_dims / 2], on the device
+    rot_dims: int
+    interleaved: bool
+
 
 class PositionEncoding(Part):
     """Encodes positions into queries and keys.
@@ -288,6 +309,11 @@ class PositionEncoding(Part):
         raise NotImplementedError
 
     def fused_rotary_table(self, head_dim: int) -> torch.Tensor | None:
+        return None
+
+    def rotary_plan(self, head_dim: int) -> RotaryPlan | None:
+        """What a mixer needs to rotate inside a kernel of its own, for encodings that are a rotation of
+        pairs (whole head or part of it, either pairing); ``None`` means "call apply()"."""
         return None
 
 
@@ -324,9 +350,12 @@ class Block(Part):
 
 @dataclass
 class ResidualStream:
-    """The fp32 residual rows plus a delta (tensor or ``SplitSum``) the next norm still has to add."""
+    """The fp32 residual rows plus a delta (tensor or ``SplitSum``) the next norm still has to add.
+    ``rounded``: the same rows (without the pending delta) in the activation type, if the part that wrote
+    them last made that copy; whoever changes ``resid`` without renewing it sets it to None."""
     resid: torch.Tensor
     pending: object = None
+    rounded: torch.Tensor | None = None
 
 
 # ---------------------------------------------------------------------------

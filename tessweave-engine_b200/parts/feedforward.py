@@ -20,8 +20,12 @@ class SwiGLU(FeedForward):
     Reference: flow_engine/model.py:68-85.
     """
 
-    def __init__(self, runtime: Runtime, hidden: int, intermediate: int):
+    NAMES = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+    def __init__(self, runtime: Runtime, hidden: int, intermediate: int, names: tuple[str, str, str] | None = None):
+        """``names``: the checkpoint's names of the gate, up and down matrices (default: the reference's)."""
         super().__init__(runtime)
+        self.names = tuple(names) if names else self.NAMES
         if min(hidden, intermediate) <= 0:
             raise ValueError("swiglu needs positive sizes")
         self.hidden, self.intermediate = hidden, intermediate
@@ -36,9 +40,9 @@ class SwiGLU(FeedForward):
             gate, up = groups[:, 0], groups[:, 1]          # [i / 8, 8, hidden] views; the loader reshapes the source
         else:
             gate, up = self.w_gate_up[:i], self.w_gate_up[i:]
-        return [WeightDecl("gate_proj.weight", (i, self.hidden), dest=gate),
-                WeightDecl("up_proj.weight", (i, self.hidden), dest=up),
-                WeightDecl("down_proj.weight", (self.hidden, i), dest=self.w_down)]
+        return [WeightDecl(self.names[0], (i, self.hidden), dest=gate),
+                WeightDecl(self.names[1], (i, self.hidden), dest=up),
+                WeightDecl(self.names[2], (self.hidden, i), dest=self.w_down)]
 
     def forward(self, ctx: StepContext, h: torch.Tensor):
         return self.down(ctx, self.gate_up(ctx, h))

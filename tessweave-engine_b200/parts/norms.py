@@ -12,7 +12,9 @@ class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * weight, statistics in fp32.
 
     Reference: flow_engine/model.py:15-23.  The pending delta of the previous
-    sub-layer is added to the residual stream in the same kernel.
+    sub-layer is added to the residual stream in the same kernel.  ``add_normed`` is the other
+    arrangement: the norm of a sub-layer's output, added to the stream.  ``weight_name`` may be
+    empty: the tensor then carries the part's own name.
     """
     accepts_split_sum = True
 
@@ -28,3 +30,6 @@ class RMSNorm(Norm):
 
     def forward(self, ctx: StepContext, out, resid, delta, n_rows, rows=None) -> None:
         ops.add_rmsnorm(out, resid, delta, self.weight, self.eps, n_rows, rows)
+
+    def add_normed(self, ctx: StepContext, resid, delta, n_rows, copy=None) -> None:
+        ops.rmsnorm_to_residual(resid, delta, self.weight, self.eps, n_rows, copy)
