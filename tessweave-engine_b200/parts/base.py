@@ -56,7 +56,7 @@ class WeightDecl:
     in 32 bits stays so; bf16 widens exactly), ``table_int`` in int32.  ``dest`` is
     the device storage the loader copies into, usually a slice of a packed buffer.
     ``init`` is the random-weights rule: ``normal`` ~ N(0, std), ``one_plus_normal``
-    ~ 1 + N(0, 0.1), ``zeros``.
+    ~ 1 + N(0, 0.1), ``eye_plus_normal`` ~ I + N(0, std), ``zeros``.
     """
     name: str
     shape: tuple[int, ...]

@@ -64,7 +64,7 @@ class SigmoidAttention(Mixer):
                  WeightDecl(nm["q_norm"], (q,), role="vector", init="one_plus_normal", dest=self.q_norm),
                  WeightDecl(nm["k_norm"], (kv,), role="vector", init="one_plus_normal", dest=self.k_norm)]
         if self.mix is not None:
-            decls.append(WeightDecl(nm["mix"], (self.n_heads, self.n_heads), role="vector", dest=self.mix))
+            decls.append(WeightDecl(nm["mix"], (self.n_heads, self.n_heads), role="vector", init="eye_plus_normal", dest=self.mix))
         if self.bias is not None:
             decls.append(WeightDecl(nm["bias"], (self.n_heads,), role="vector", dest=self.bias))
         if self.gate_size:

@@ -3,7 +3,7 @@
 Every tensor is drawn on the CPU from its own generator, seeded by (seed, tensor
 name), so any subset of tensors can be reproduced alone.  The rule per tensor is
 the declaration's: matrices, embeddings and biases ~ N(0, std); norm weights
-~ 1 + N(0, 0.1).  The reference has no such mode (its tests take random weights
+~ 1 + N(0, 0.1); square matrices that mix heads ~ I + N(0, std).  The reference has no such mode (its tests take random weights
 from a library model: tests/test_engine.py:15-25).
 
 ``fill_random`` draws the same kind of weights straight into a model's device
@@ -42,6 +42,8 @@ def draw(decl: WeightDecl, seed: int, std: float) -> torch.Tensor:
         return 1.0 + NORM_WEIGHT_STD * noise
     if decl.init == "normal":
         return std * noise
+    if decl.init == "eye_plus_normal":
+        return torch.eye(decl.shape[0], decl.shape[1]) + std * noise
     raise ValueError(f"unknown init rule {decl.init!r} for {decl.name}")
 
 
@@ -85,6 +87,10 @@ def fill_random(model: Model, seed: int = 0, std: float | None = None) -> Model:
             continue
         if decl.role == "table_int":
             decl.dest.copy_(torch.randint(0, 2 ** 15, decl.shape, generator=g, device=device, dtype=torch.int32))
+            continue
+        if decl.init == "eye_plus_normal":
+            noise = torch.randn(decl.shape, generator=g, device=device, dtype=torch.float32)
+            decl.dest.copy_(torch.eye(decl.shape[0], decl.shape[1], device=device) + std * noise)
             continue
         rows = decl.dest.shape[0]
         step = max(1, (64 << 20) // max(1, decl.dest[0].numel() if decl.dest.dim() > 1 else 1))

@@ -166,5 +166,5 @@ def replay_in_process(folder, dtype: str, steps: list[dict], out_dir, max_tokens
     assert code == 0, f"replay exited with {code}"
     done = [line for line in stdout.getvalue().splitlines() if line.startswith("done ")]
     assert len(done) == len(steps), "replay did not report every step"
-    vocab = json.loads((Path(folder) / "config.json").read_text())["vocab_size"]
-    return collect(steps, out_dir, vocab)
+    config = json.loads((Path(folder) / "config.json").read_text())
+    return collect(steps, out_dir, config["vocab_size"] if "vocab_size" in config else config["vocab"])
