@@ -213,6 +213,79 @@ def sigmoid_attention_generic(out: torch.Tensor, qf: torch.Tensor, bias: torch.T
     _check(code, "sigmoid_attention_generic")
 
 
+def sigmoid_attention_tensor_cores(dtype: torch.dtype, head_dim: int, n_kv_heads: int) -> bool:
+    """Whether the tensor-core kernels (csrc/sigmoid_attention_bf16.cu) take the shape: bfloat16, a head size that is a
+    multiple of 16 up to 256, and a tile of 64 folded queries plus the ring of key chunks within 227 KB of shared
+    memory.  TESSWEAVE_SIGMOID_ATTENTION=exact sends everything to the exact kernel."""
+    import os
+    if os.environ.get("TESSWEAVE_SIGMOID_ATTENTION") == "exact":
+        return False
+    if dtype != torch.bfloat16 or head_dim % 16 or not 16 <= head_dim <= 256:
+        return False
+    return 64 * (n_kv_heads * head_dim + 8) * 2 + 3 * 64 * (head_dim + 8) * 2 <= 227 * 1024
+
+
+def sigmoid_decode_splits(n_seqs: int, n_heads: int, max_kv_len: int) -> int:
+    """Slices a single token's keys are cut into: enough blocks (request x 16 heads x slice) for two per SM,
+    at least two tiles of 64 keys per slice, at most 64 slices."""
+    import os
+    forced = os.environ.get("TESSWEAVE_SIGMOID_DECODE_SPLITS")
+    tiles = max(1, -(-max_kv_len // 64))
+    if forced:
+        return max(1, min(int(forced), 64, tiles))
+    groups = max(1, n_seqs * -(-n_heads // 16))
+    return max(1, min((2 * _SM_COUNT) // groups, tiles // 2, 64))
+
+
+def _sigattn_checks(out, qf, bias, gate, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim):
+    _cuda(out, qf, bias, gate, block_table, k_pages, v_pages)
+    _need(out.dtype == torch.bfloat16 and qf.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
+          and v_pages.dtype == torch.bfloat16, "sigmoid attention (tensor cores): operands must be bfloat16")
+    _need(out.stride(1) == 1 and qf.is_contiguous() and qf.data_ptr() % 16 == 0, "sigmoid attention: bad out / folded queries")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and v_pages.shape == k_pages.shape
+          and tuple(k_pages.shape[1:]) == (n_kv_heads, k_pages.shape[2], head_dim) and k_pages.data_ptr() % 16 == 0
+          and v_pages.data_ptr() % 16 == 0, "sigmoid attention: cache pages must be contiguous [pages, kv_heads, page, head_dim]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == n_q_heads), "sigmoid attention: bias must be fp32 [Hq]")
+    _need(gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape[1] >= n_q_heads * head_dim
+                           and gate.data_ptr() % 4 == 0 and gate.stride(0) % 2 == 0),
+          "sigmoid attention: gate must be bfloat16 [rows, Hq * D]")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "sigmoid attention: bad block table")
+    _need(n_q_heads % n_kv_heads == 0, "sigmoid attention: query heads must be a multiple of key/value heads")
+
+
+def sigmoid_attention_prefill(out, qf, bias, gate, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, k_pages,
+                              v_pages, n_seqs: int, max_q_len: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                              window: int, skip_singles: bool, status: torch.Tensor) -> None:
+    """Tensor-core sigmoid attention for the requests of a step that bring several tokens (and, unless
+    ``skip_singles``, those that bring one): out[row, h] = (sum of sigmoid(qf . k + bias) v) * sigmoid(gate)."""
+    _sigattn_checks(out, qf, bias, gate, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
+    code = _fn("sigmoid_attention_bf16", "tw_sigattn_prefill", {"TW_HEAD_DIM": head_dim})(
+        _ptr(out), c_int(out.stride(0)), _ptr(qf), _ptr(bias), _ptr(gate), c_int(0 if gate is None else gate.stride(0)),
+        _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table),
+        c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_seqs), c_int(max_q_len), c_int(n_q_heads),
+        c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), c_int(window), c_int(1 if skip_singles else 0),
+        _ptr(status), _stream())
+    _check(code, "sigmoid_attention_prefill")
+
+
+def sigmoid_attention_decode(out, partial, qf, bias, gate, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
+                             k_pages, v_pages, n_seqs: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int,
+                             nsplit: int, status: torch.Tensor) -> None:
+    """Tensor-core sigmoid attention for the requests of a step that bring one token, their keys cut into
+    ``nsplit`` slices; ``partial`` is fp32 scratch of at least n_seqs * nsplit * Hq * D values."""
+    _sigattn_checks(out, qf, bias, gate, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
+    _need(partial.dtype == torch.float32 and partial.is_contiguous()
+          and partial.numel() >= n_seqs * nsplit * n_q_heads * head_dim and 1 <= nsplit <= 64,
+          "sigmoid attention: scratch must be fp32 [requests, slices, Hq, D], 1 to 64 slices")
+    code = _fn("sigmoid_attention_bf16", "tw_sigattn_decode", {"TW_HEAD_DIM": head_dim})(
+        _ptr(out), c_int(out.stride(0)), _ptr(partial), _ptr(qf), _ptr(bias), _ptr(gate),
+        c_int(0 if gate is None else gate.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(seq_slot),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_seqs), c_int(n_q_heads),
+        c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), c_int(window), c_int(nsplit), _ptr(status),
+        _stream())
+    _check(code, "sigmoid_attention_decode")
+
+
 # ---------------------------------------------------------------------------
 # gated recurrences with a fixed-size state per request (csrc/recurrent.cu)
 # ---------------------------------------------------------------------------

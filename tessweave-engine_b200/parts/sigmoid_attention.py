@@ -105,9 +105,27 @@ class SigmoidAttention(Mixer):
         qf = self.prepare(ctx, proj, cache, write_cache)
         out = ctx.workspace.get("sigattn.out", (n, self.q_size), self.runtime.dtype)
         gate = proj[:, self.q_size + self.kv_size:] if self.gate_size else None
-        ops.sigmoid_attention_generic(out, qf, self.bias, gate, ctx.positions, ctx.seq_of_token, ctx.seq_slot,
-                                      cache.block_table, cache.k_pages, cache.v_pages, n, self.n_heads, self.n_kv_heads,
-                                      self.head_dim, self.window or 0, ctx.status)
+        window = self.window or 0
+        if not ops.sigmoid_attention_tensor_cores(self.runtime.dtype, self.head_dim, self.n_kv_heads):
+            # float32, and shapes the tensor-core kernels do not take: one block per (token, head)
+            ops.sigmoid_attention_generic(out, qf, self.bias, gate, ctx.positions, ctx.seq_of_token, ctx.seq_slot,
+                                          cache.block_table, cache.k_pages, cache.v_pages, n, self.n_heads, self.n_kv_heads,
+                                          self.head_dim, window, ctx.status)
+            return out
+        # bfloat16: portions on the tile kernel, single tokens on the kernel that cuts their keys into slices; both
+        # read the same flat batch and skip the other's requests
+        singles = ctx.decode_only or ctx.fixed_shape or any(count == 1 for count in ctx.host_q_len)
+        if not ctx.decode_only:
+            ops.sigmoid_attention_prefill(out, qf, self.bias, gate, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
+                                          ctx.seq_slot, cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs,
+                                          ctx.max_q_len, self.n_heads, self.n_kv_heads, self.head_dim, window, singles,
+                                          ctx.status)
+        if singles:
+            nsplit = ops.sigmoid_decode_splits(ctx.n_seqs, self.n_heads, ctx.max_kv_len)
+            partial = ctx.workspace.get("sigattn.partial", (ctx.n_seqs, nsplit, self.n_heads, self.head_dim), torch.float32)
+            ops.sigmoid_attention_decode(out, partial, qf, self.bias, gate, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
+                                         ctx.seq_slot, cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs,
+                                         self.n_heads, self.n_kv_heads, self.head_dim, window, nsplit, ctx.status)
         return out
 
     def project_out(self, ctx: StepContext, out: torch.Tensor):

@@ -53,8 +53,9 @@ def rotate_interleaved(t: torch.Tensor, positions: torch.Tensor, dims: int, base
     return out
 
 
-def sigmoid_attention(x: torch.Tensor, w: dict, p: dict, eps: float, start: int = 0) -> torch.Tensor:
-    """x: [T, width] rows of one sequence whose first row sits at position ``start`` (always 0 here)."""
+def sigmoid_attention(x: torch.Tensor, w: dict, p: dict, eps: float, start: int = 0, window: int | None = None) -> torch.Tensor:
+    """x: [T, width] rows of one sequence whose first row sits at position ``start`` (always 0 here).
+    ``window`` (not part of the design; the engine's mixer has it as an option): only keys j > i - window."""
     T = x.shape[0]
     H, G, D = p["heads"], p["kv_heads"], p["dim"]
     q = x @ w["q"].T
@@ -72,6 +73,8 @@ def sigmoid_attention(x: torch.Tensor, w: dict, p: dict, eps: float, start: int 
     s = torch.einsum("hg,gij->hij", w["talk"], s)
     weight = torch.sigmoid(s + w["pb"][:, None, None])
     visible = torch.ones(T, T, dtype=torch.bool).tril()
+    if window is not None:
+        visible = visible & ~torch.ones(T, T, dtype=torch.bool).tril(-window)
     weight = weight * visible
     o = torch.einsum("hij,jhd->ihd", weight, vh).reshape(T, H * D)
     o = o * torch.sigmoid(x @ w["g"].T)

@@ -132,8 +132,9 @@ def test_scaled_embedding_and_tied_head(dtype):
     close(logits.cpu(), y.float().cpu() @ emb.weight.float().cpu().t(), dtype, "tied head reads the unscaled matrix", bf16=2e-3)
 
 
-ATTENTION_SHAPES = [  # hidden, heads, kv heads, head size, rotated dims, page
-    (48, 4, 2, 16, 8, 8), (40, 3, 1, 24, 24, 4), (64, 1, 1, 32, 0, 8), (96, 6, 6, 16, 16, 16), (128, 12, 2, 64, 32, 16),
+ATTENTION_SHAPES = [  # hidden, heads, kv heads, head size, rotated dims, page, window
+    (48, 4, 2, 16, 8, 8, None), (40, 3, 1, 24, 24, 4, None), (64, 1, 1, 32, 0, 8, None), (96, 6, 6, 16, 16, 16, None),
+    (128, 12, 2, 64, 32, 16, None), (128, 20, 4, 32, 16, 8, None), (48, 4, 2, 16, 8, 8, 11), (40, 3, 1, 24, 24, 4, 7),
 ]
 
 
@@ -142,10 +143,10 @@ ATTENTION_SHAPES = [  # hidden, heads, kv heads, head size, rotated dims, page
 def test_sigmoid_attention_alone(dtype, shape):
     """The mixer on hand-made rows: a portion of request a beside a single token of request b, whose earlier
     keys an earlier call wrote; then a's next portion.  Against the plain mixer on each whole sequence."""
-    hidden, heads, kv, d, rot, page = shape
+    hidden, heads, kv, d, rot, page, window = shape
     rt = Runtime(torch.device("cuda"), dtype)
     spec = PartSpec("sigmoid_attention", {"hidden": hidden, "n_heads": heads, "n_kv_heads": kv, "head_dim": d,
-                                          "scale": 1.5 / d ** 0.5, "eps": 1e-5,
+                                          "scale": 1.5 / d ** 0.5, "eps": 1e-5, "window": window,
                                           "position": PartSpec("rope_interleaved", {"theta": 500.0, "dims": rot})})
     mixer = build_part("mixer", spec, rt)
     w = fill(mixer, 6, 0.3)
@@ -156,8 +157,8 @@ def test_sigmoid_attention_alone(dtype, shape):
     a, b = cache.admit(None), cache.admit(None)
     g = torch.Generator().manual_seed(7)
     ha, hb = (torch.randn(30, hidden, generator=g)).to(dtype), (torch.randn(20, hidden, generator=g)).to(dtype)
-    want_a = plain.sigmoid_attention(ha.float(), w, params, 1e-5)
-    want_b = plain.sigmoid_attention(hb.float(), w, params, 1e-5)
+    want_a = plain.sigmoid_attention(ha.float(), w, params, 1e-5, window=window)
+    want_b = plain.sigmoid_attention(hb.float(), w, params, 1e-5, window=window)
 
     def run(ctx, h):
         cache.sync_tables()
@@ -176,6 +177,41 @@ def test_sigmoid_attention_alone(dtype, shape):
     close(got[:13], want_a[:13], dtype, "a's first portion beside b")
     close(got[13:], want_b[19:], dtype, "b's single token beside a")
     close(got_a1, want_a[13:], dtype, "a's second portion")
+
+
+@pytest.mark.parametrize("heads,kv,d,window", [(8, 2, 64, None), (20, 4, 32, None), (3, 1, 96, None), (4, 4, 128, 150), (2, 1, 16, 65)])
+def test_tensor_core_attention_against_the_exact_kernel(heads, kv, d, window, monkeypatch):
+    """bfloat16, several hundred keys: portions whose tiles end inside pages and inside tiles of 64 keys, and
+    single tokens whose keys are cut into slices, through the tensor-core kernels and through the exact kernel
+    (same rounded inputs, so they differ by the rounding of the weights to bfloat16 and no more)."""
+    hidden, page = 64, 16
+    rt = Runtime(torch.device("cuda"), torch.bfloat16)
+    spec = PartSpec("sigmoid_attention", {"hidden": hidden, "n_heads": heads, "n_kv_heads": kv, "head_dim": d,
+                                          "scale": 1.2 / d ** 0.5, "eps": 1e-5, "window": window,
+                                          "position": PartSpec("rope_interleaved", {"theta": 1e4, "dims": d // 2})})
+    g = torch.Generator().manual_seed(5)
+    rows = torch.randn(700, hidden, generator=g).to(torch.bfloat16)
+    cuts = [200, 1, 57, 130, 1, 1, 64, 1, 193, 1, 1, 50]
+    results = {}
+    for mode in ("tensor", "exact"):
+        if mode == "exact":
+            monkeypatch.setenv("TESSWEAVE_SIGMOID_ATTENTION", "exact")
+        mixer = build_part("mixer", spec, rt)
+        fill(mixer, 21, 0.3)
+        mixer.bias.fill_(-2.0)
+        cache = tw.CacheManager([(mixer.cache_need(), None)], page, 48, 1, 768, torch.bfloat16, rt.device, prefix_cache=False)
+        lease = cache.admit(None)
+        outs, p = [], 0
+        for n in cuts:
+            cache.ensure(lease, p + n)
+            cache.sync_tables()
+            ctx = ctx_of(rt, list(range(p, p + n)), [0] * n, [lease.slot], [0], [n], [p + n])
+            outs.append(mixer.attend(ctx, mixer.project_in(ctx, rows[p:p + n].cuda()), cache.view(0), True).float().cpu().clone())
+            assert int(ctx.status) == 0
+            p += n
+        results[mode] = torch.cat(outs)
+    scale = float(results["exact"].abs().max())
+    assert float((results["tensor"] - results["exact"]).abs().max()) <= 0.02 * scale
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
