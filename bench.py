@@ -350,6 +350,47 @@ def workload_run(name: str, layers: int | None) -> dict:
             "finished": stats["finished"], "weights_gb": round(model.weight_bytes() / 1e9, 2)}
 
 
+def design_run(args, pk: dict, pk_source: str) -> dict:
+    """``--design linurax``: the Linurax decoder and the Qwen2 decoder at the layer sizes of the benchmark
+    configuration (``--layers`` of them, default 8 here), random weights: a prompt step of 2,048 tokens, decode at
+    batch 1 and ``--batch`` with ``--context`` keys, and the Linurax kernels alone."""
+    import torch
+    import tessweave_engine_b200 as tw
+    from tessweave_engine_b200.engine import design_bench as db
+    from tessweave_engine_b200.engine.kernel_bench import format_table, kernel_table
+    layers = args.layers if args.layers != BENCH_CONFIG["num_hidden_layers"] else 8
+    sizes = {"7b": BENCH_CONFIG, **{k: dict(BENCH_CONFIG, **v) for k, v in DESIGN_SIZES.items()}}
+    record = {"design": args.design, "layers": layers, "batch": args.batch, "context": args.context,
+              "prefill_tokens": PREFILL_TOKENS, "peaks": pk, "peaks_source": pk_source, "dtype": "bf16",
+              "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
+    for name, qwen in sizes.items():
+        entry = {}
+        for design, config in (("linurax", db.linurax_config_like(qwen, layers)), ("qwen2", dict(qwen, num_hidden_layers=layers))):
+            model = db.build(config)
+            t = db.step_times(model, args.batch, args.context, PREFILL_TOKENS, PAGE_SIZE)
+            for b in sorted({1, args.batch}):
+                t[f"decode_b{b}_hbm_frac"] = round(t[f"decode_b{b}_step_bytes"] / (t[f"decode_b{b}_ms"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+            entry[design] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in t.items()}
+            del model
+            torch.cuda.empty_cache()
+        record["sizes"][name] = entry
+    _, spec = tw.resolve(db.linurax_config_like(BENCH_CONFIG, 4))
+    rows = db.linurax_kernel_table(spec, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
+    _, qspec = tw.resolve(BENCH_CONFIG)
+    qrows = kernel_table(qspec, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE,
+                         only=("attention", "RMSNorm"))
+    print(format_table(rows + qrows), file=sys.stderr)
+    record["kernels"] = rows
+    record["qwen2_like_kernels"] = qrows
+    return record
+
+
+# Further layer sizes of the design comparison (overrides of the benchmark configuration).
+DESIGN_SIZES = {
+    "1.5b": {"hidden_size": 1536, "intermediate_size": 8960, "num_attention_heads": 12, "num_key_value_heads": 2},
+}
+
+
 def config_record(args, peaks_source: str) -> dict:
     """What both arms measure on (flat, every size named): the same record in the line of either arm."""
     c = BENCH_CONFIG
@@ -434,6 +475,10 @@ def main() -> int:
     ap.add_argument("--timeline", action="store_true",
                     help="record one decode step block by block on the device (kernels compiled with their recorder) "
                          "and print its launches in time order; for looking at, not a measurement")
+    ap.add_argument("--design", choices=["linurax"], default=None,
+                    help="another design beside the Qwen2 decoder at equal layer sizes: prompt and decode throughput of "
+                         "both, and the design's own kernels with their rooflines (a record of its own; the default "
+                         "workload and its JSON line are not touched)")
     ap.add_argument("--workload", choices=sorted(WORKLOAD_SIZES), default=None,
                     help="run a whole-engine workload at 14B / 32B layer sizes instead of the headline measurement")
     args = ap.parse_args()
@@ -452,6 +497,9 @@ def main() -> int:
         print(json.dumps(workload_run(args.workload, args.layers if args.layers != BENCH_CONFIG["num_hidden_layers"] else None)))
         return 0
     pk, pk_source = peaks()
+    if args.design:
+        print(json.dumps(design_run(args, pk, pk_source)))
+        return 0
     if args.kernels:
         import tessweave_engine_b200 as tw
         from tessweave_engine_b200.engine.kernel_bench import format_table, kernel_table

@@ -291,10 +291,11 @@ def sigmoid_attention_decode(out, partial, qf, bias, gate, seq_q_start, seq_q_le
 # ---------------------------------------------------------------------------
 def mingru_scan(out: torch.Tensor, proj: torch.Tensor, bias_z: torch.Tensor | None, bias_x: torch.Tensor | None,
                 state: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor,
-                n_seqs: int, width: int, write_state: bool = True) -> None:
+                n_seqs: int, max_q_len: int, width: int, write_state: bool = True) -> None:
     """Rows of ``proj`` are [z | x | g] pre-activations (each ``width`` wide); for every request of the step the
     state S (fp32 [slots, width], row ``seq_slot``) runs through its rows: S = (1 - z) S + z c, and
-    out = S * silu(g) in the type of ``out``."""
+    out = S * silu(g) in the type of ``out``.  ``max_q_len`` (the longest portion of the step) chooses between one
+    thread per channel and a block that cuts a long portion into segments."""
     _cuda(out, proj, bias_z, bias_x, state, seq_slot, seq_q_start, seq_q_len)
     _need(proj.stride(1) == 1 and proj.shape[1] >= 3 * width and out.stride(1) == 1 and out.shape[1] >= width
           and out.dtype == proj.dtype, "mingru: rows must be [z | x | g] and the output of the same type")
@@ -303,7 +304,8 @@ def mingru_scan(out: torch.Tensor, proj: torch.Tensor, bias_z: torch.Tensor | No
         _need(b is None or (b.dtype == torch.float32 and b.numel() == width), "mingru: biases must be fp32 [width]")
     code = _fn("recurrent", "tw_mingru_scan")(
         _ptr(out), c_int(out.stride(0)), _ptr(proj), c_int(proj.stride(0)), _ptr(bias_z), _ptr(bias_x), _ptr(state),
-        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(width), c_int(1 if write_state else 0),
+        _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(max_q_len), c_int(width),
+        c_int(1 if write_state else 0),
         c_int(dtype_code(out.dtype)), _stream())
     _check(code, "mingru_scan")
 

@@ -1,0 +1,200 @@
+"""Two designs side by side at equal layer sizes: whole-step throughput (a prompt step, decode steps) of
+each, and the kernels of the Linurax design alone with their rooflines.
+
+The Linurax model of the comparison has the residual width, head counts, head size, feed-forward size and
+vocabulary of the Qwen2 benchmark configuration; its layers alternate [attention + feed-forward, mingru,
+mingru, attention + feed-forward], the recurrent width equals the residual width.  Weights are random.
+``python bench.py --design linurax`` prints the record.
+"""
+from __future__ import annotations
+
+import statistics
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..csrc import ops
+from ..parts.base import Runtime, StateView, Workspace, build_part
+from .kernel_bench import _context, _copies, _fill, _graph_us, _kernels_of
+
+
+def linurax_config_like(qwen: dict, layers: int) -> dict:
+    """A Linurax config.json with the sizes of the Qwen2 configuration ``qwen``."""
+    heads, kv, dim = qwen["num_attention_heads"], qwen["num_key_value_heads"], qwen["head_dim"]
+    attention = {"type": "attention",
+                 "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                           "rot": {"dims": dim, "base": qwen["rope_theta"]}},
+                 "mlp": {"kind": "dense", "ff": qwen["intermediate_size"]}}
+    recurrent = {"type": "mingru", "mixer": {"width": qwen["hidden_size"]}, "mlp": None}
+    pattern = [attention, recurrent, recurrent, attention]
+    return {"architecture": "Linurax", "vocab": qwen["vocab_size"], "width": qwen["hidden_size"],
+            "embedding": {"scale": 1.0}, "norm": {"eps": qwen["rms_norm_eps"]},
+            "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def build(config: dict):
+    import tessweave_engine_b200 as tw
+    cfg, spec = tw.resolve(config)
+    model = tw.Model(spec, Runtime(torch.device("cuda:0"), torch.bfloat16), config=cfg)
+    tw.fill_random(model, seed=0)
+    return model
+
+
+def step_times(model, batch: int, context: int, prefill_tokens: int, page_size: int, steps: int = 24, warmup: int = 4) -> dict:
+    """Median time of a prompt step of ``prefill_tokens`` tokens, and time per decode step of ``batch``
+    requests that hold ``context`` tokens each (CUDA graphs, random cache contents)."""
+    from .runner import ModelRunner, StepEntry
+    vocab = model.spec.vocab_size
+    out = {}
+    # ---- a prompt step
+    cache = CacheManager(model.cache_needs(), page_size, -(-prefill_tokens // page_size), 1, prefill_tokens,
+                         model.runtime.dtype, model.runtime.device, prefix_cache=False)
+    runner = ModelRunner(model, cache, max_step_tokens=prefill_tokens, max_step_seqs=1, max_logit_rows=1, cuda_graphs=False)
+    lease = cache.admit(None)
+    cache.ensure(lease, prefill_tokens)
+    ids = torch.randint(0, vocab, (prefill_tokens,), generator=torch.Generator().manual_seed(2)).tolist()
+    entry = [StepEntry(lease.slot, ids, 0, [prefill_tokens - 1])]
+    for _ in range(3):
+        runner.step(entry)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(5):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        runner.step(entry)
+        end.record()
+        torch.cuda.synchronize()
+        times.append(begin.elapsed_time(end))
+    runner.check_status()
+    out["prefill_ms"] = statistics.median(times)
+    out["prefill_tok_s"] = prefill_tokens / (out["prefill_ms"] / 1e3)
+    del runner, cache
+    torch.cuda.empty_cache()
+    # ---- decode steps
+    for b in sorted({1, batch}):
+        total = warmup + steps
+        start = max(1, context - total)
+        cache = CacheManager(model.cache_needs(), page_size, b * (-(-(start + total) // page_size)), b, start + total,
+                             model.runtime.dtype, model.runtime.device, prefix_cache=False)
+        for g in cache.groups:
+            g.k.normal_(0, 0.5)
+            g.v.normal_(0, 0.5)
+        runner = ModelRunner(model, cache, max_step_tokens=b, max_step_seqs=b, cuda_graphs=True)
+        leases = [cache.admit(None) for _ in range(b)]
+        for lease in leases:
+            cache.ensure(lease, start + total)
+        tokens = torch.randint(0, vocab, (total, b), generator=torch.Generator().manual_seed(1)).tolist()
+
+        def one(i):
+            return runner.step([StepEntry(leases[r].slot, [tokens[i][r]], start + i, [0]) for r in range(b)])
+
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for i in range(warmup, total):
+            one(i)
+        end.record()
+        torch.cuda.synchronize()
+        runner.check_status()
+        ms = begin.elapsed_time(end) / steps
+        element = 2
+        nbytes = model.step_weight_bytes(b) + b * (start + warmup + steps / 2) * model.cache_bytes_per_token(element)
+        out[f"decode_b{b}_ms"] = ms
+        out[f"decode_b{b}_tok_s"] = b / (ms / 1e3)
+        out[f"decode_b{b}_step_bytes"] = nbytes
+        bucket = next((k for k in sorted(runner.graph_kernels) if k >= b), None)
+        out[f"decode_b{b}_kernels"] = runner.graph_kernels.get(bucket)
+        del runner, cache
+        torch.cuda.empty_cache()
+    return out
+
+
+def linurax_kernel_table(spec, batch: int, context: int, prefill_tokens: int, hbm_gbs: float, tflops: float,
+                         page_size: int = 16) -> list[dict]:
+    """The Linurax kernels alone, each inside a CUDA graph with operands rotated beyond L2: preparation of queries
+    and keys, attention over the cache, the recurrence, the norm into the stream; decode (``batch`` rows) and a
+    prompt step.  fraction = max(bytes / HBM peak, FLOPs / tensor peak) / time."""
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    rt = Runtime(dev, bf)
+    att_spec = next(l.block.params["mixer"] for l in spec.layers if l.block.params["mixer"].kind == "sigmoid_attention")
+    rec_spec = next(l.block.params["mixer"] for l in spec.layers if l.block.params["mixer"].kind == "mingru")
+    norm_spec = spec.layers[0].block.params["norm1"]
+    H = spec.hidden_size
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows: list[dict] = []
+
+    def add(name, m, thunks, nbytes, flops, reps=4):
+        kernel = _kernels_of(thunks[0])
+        us = _graph_us(thunks, reps)
+        floor = max(nbytes / (hbm_gbs * 1e9), flops / (tflops * 1e12)) * 1e6
+        rows.append({"op": name, "rows": m, "kernel": kernel, "us": round(us, 2), "mbytes": round(nbytes / 1e6, 2),
+                     "gflop": round(flops / 1e9, 2), "floor_us": round(floor, 2), "frac": round(floor / us, 3),
+                     "bound": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (tflops * 1e12) else "tensor"})
+
+    for m, phase in ((batch, "decode"), (prefill_tokens, "prefill")):
+        ws = Workspace(dev)
+        if phase == "decode":
+            ctx = _context(rt, ws, status, [context - 1] * m, list(range(m)), list(range(m)), list(range(m)), [1] * m, [context] * m)
+        else:
+            ctx = _context(rt, ws, status, list(range(m)), [0] * m, [0], [0], [m], [m])
+        # ---- norm of a sub-layer's output into the stream
+        norm = build_part("norm", norm_spec, rt)
+        _fill(norm)
+        sets = [(torch.randn(m, H, device=dev), torch.randn(m, H, device=dev, dtype=bf), torch.empty(m, H, device=dev, dtype=bf))
+                for _ in range(_copies(m * H * 12))]
+        add(f"{phase}: RMSNorm of the output + residual add", m,
+            [(lambda r=r, d=d, c=c: norm.add_normed(ctx, r, d, m, c)) for r, d, c in sets], m * H * (2 + 4 + 4 + 2), 0.0, reps=8)
+        del sets
+        # ---- attention: preparation, then the keys
+        att = build_part("mixer", att_spec, rt)
+        _fill(att)
+        att.mix.copy_(torch.eye(att.n_heads, device=dev) + 0.05 * torch.randn(att.n_heads, att.n_heads, device=dev))
+        Hq, G, D = att.n_heads, att.n_kv_heads, att.head_dim
+        requests = batch if phase == "decode" else 1
+        kv_tokens = context if phase == "decode" else m
+        blocks = -(-kv_tokens // page_size)
+        page_bytes = 2 * requests * blocks * page_size * G * D * 2
+        caches = []
+        for _ in range(_copies(page_bytes)):
+            cache = CacheManager([(att.cache_need(), None)], page_size, requests * blocks, requests, kv_tokens, bf, dev,
+                                 prefix_cache=False)
+            for g in cache.groups:
+                g.k.normal_(0, 0.5)
+                g.v.normal_(0, 0.5)
+            for _r in range(requests):
+                cache.ensure(cache.admit(None), kv_tokens)
+            cache.sync_tables()
+            caches.append(cache)
+        views = [c.view(0) for c in caches]
+        in_w = att.q_size + att.kv_size + att.gate_size
+        projs = [torch.randn(m, in_w, device=dev, dtype=bf) for _ in range(_copies(m * in_w * 2) if phase == "prefill" else 1)]
+        add(f"{phase}: q/k norms + rotation + cache write + fold of the heads' mixing", m,
+            [(lambda v=v, i=i: att.prepare(ctx, projs[i % len(projs)], v, True)) for i, v in enumerate(views)],
+            m * (att.q_size + att.kv_size) * 2 + m * 2 * att.kv_size * 2 + m * Hq * att.kv_size * 2, 2.0 * m * Hq * Hq * D)
+        qf = att.prepare(ctx, projs[0], views[0], True).clone()
+        if phase == "decode":
+            nbytes = m * context * G * D * 2 * 2 + m * Hq * att.kv_size * 2
+            flops = 2.0 * m * Hq * (att.kv_size + D) * context
+            name = f"decode: sigmoid attention over {context} keys + output gate"
+        else:
+            nbytes = m * Hq * att.kv_size * 2 + 2 * m * att.kv_size * 2 + m * att.q_size * 2 * 2
+            flops = 2.0 * Hq * (att.kv_size + D) * m * (m + 1) / 2
+            name = f"prefill: causal sigmoid attention + output gate, {m} tokens"
+        add(name, m, [(lambda v=v, i=i: att.attend_prepared(ctx, qf, projs[i % len(projs)], v)) for i, v in enumerate(views)],
+            nbytes, flops)
+        del caches, views, projs, att
+        # ---- the recurrence
+        rec = build_part("mixer", rec_spec, rt)
+        _fill(rec)
+        W = rec.width
+        state = StateView(torch.zeros(max(requests, 1), W, device=dev))
+        projs = [torch.randn(m, 3 * W, device=dev, dtype=bf) for _ in range(_copies(m * 3 * W * 2) if phase == "prefill" else 1)]
+        add(f"{phase}: minGRU gates + recurrence + output gate", m, [(lambda p=p: rec.recur(ctx, p, state)) for p in projs],
+            m * 3 * W * 2 + m * W * 2 + 2 * requests * W * 4, 0.0, reps=8)
+        del projs, rec
+        torch.cuda.empty_cache()
+    if int(status) != 0:
+        raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
+    return rows

@@ -61,7 +61,7 @@ class MinGRU(Mixer):
         """[rows, width]: S_t * silu(gate) for the step's rows; the requests' states move on."""
         out = ctx.workspace.get("mingru.out", (ctx.n_tokens, self.width), self.runtime.dtype)
         ops.mingru_scan(out, proj, self.b_z, self.b_x, cache.state, ctx.seq_slot, ctx.seq_q_start, ctx.seq_q_len,
-                        ctx.n_seqs, self.width, write_state)
+                        ctx.n_seqs, ctx.max_q_len, self.width, write_state)
         return out
 
     def project_out(self, ctx: StepContext, out: torch.Tensor):

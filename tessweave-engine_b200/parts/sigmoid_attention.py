@@ -101,8 +101,11 @@ class SigmoidAttention(Mixer):
 
     def attend(self, ctx: StepContext, proj: torch.Tensor, cache: PagedView, write_cache: bool) -> torch.Tensor:
         """[rows, Hq * D]: the gated heads of the step's rows."""
+        return self.attend_prepared(ctx, self.prepare(ctx, proj, cache, write_cache), proj, cache)
+
+    def attend_prepared(self, ctx: StepContext, qf: torch.Tensor, proj: torch.Tensor, cache: PagedView) -> torch.Tensor:
+        """The attention itself, over the cache as ``prepare`` left it; the gate is read from ``proj``."""
         n = ctx.n_tokens
-        qf = self.prepare(ctx, proj, cache, write_cache)
         out = ctx.workspace.get("sigattn.out", (n, self.q_size), self.runtime.dtype)
         gate = proj[:, self.q_size + self.kv_size:] if self.gate_size else None
         window = self.window or 0

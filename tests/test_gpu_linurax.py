@@ -217,18 +217,19 @@ def test_tensor_core_attention_against_the_exact_kernel(heads, kv, d, window, mo
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hidden,width", [(48, 80), (40, 33), (128, 300)])
 def test_mingru_alone(dtype, hidden, width):
-    """The recurrence cut into steps (down to one row), two requests side by side, the state carried in slots."""
+    """The recurrence cut into steps (down to one row, up to 150), two requests side by side, the state carried in slots."""
     rt = Runtime(torch.device("cuda"), dtype)
     mixer = build_part("mixer", PartSpec("mingru", {"hidden": hidden, "width": width}), rt)
     w = fill(mixer, 11, 0.4)
     state = torch.zeros(3, width, device="cuda")
     view = tw.parts.StateView(state)
     g = torch.Generator().manual_seed(3)
-    ha, hb = torch.randn(23, hidden, generator=g).to(dtype), torch.randn(9, hidden, generator=g).to(dtype)
+    ha, hb = torch.randn(223, hidden, generator=g).to(dtype), torch.randn(9, hidden, generator=g).to(dtype)
     want_a, want_b = plain.mingru(ha.float(), w), plain.mingru(hb.float(), w)
     got_a, got_b = [], []
     # (rows of a, rows of b) per step; a sits in slot 2, b in slot 0
-    plan = [(7, 0), (1, 4), (2, 1), (0, 1), (13, 3)]
+    # a portion of more than 64 rows is cut into segments that are chained inside the kernel
+    plan = [(7, 0), (1, 4), (2, 1), (0, 1), (150, 3), (63, 0)]
     pa = pb = 0
     for na, nb in plan:
         rows = [ha[pa:pa + na], hb[pb:pb + nb]]
