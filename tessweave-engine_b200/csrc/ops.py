@@ -226,14 +226,14 @@ def sigmoid_attention_tensor_cores(dtype: torch.dtype, head_dim: int, n_kv_heads
 
 
 def sigmoid_decode_splits(n_seqs: int, n_heads: int, max_kv_len: int) -> int:
-    """Slices a single token's keys are cut into: enough blocks (request x 16 heads x slice) for two per SM,
+    """Slices a single token's keys are cut into: enough blocks (request x up to 32 heads x slice) for two per SM,
     at least two tiles of 64 keys per slice, at most 64 slices."""
     import os
     forced = os.environ.get("TESSWEAVE_SIGMOID_DECODE_SPLITS")
     tiles = max(1, -(-max_kv_len // 64))
     if forced:
         return max(1, min(int(forced), 64, tiles))
-    groups = max(1, n_seqs * -(-n_heads // 16))
+    groups = max(1, n_seqs * -(-n_heads // (32 if n_heads > 16 else 16)))
     return max(1, min((2 * _SM_COUNT) // groups, tiles // 2, 64))
 
 

@@ -70,7 +70,27 @@ mingru_scan_segments_kernel(T* __restrict__ out, int out_stride, const T* __rest
     const float bz = (live && bias_z) ? bias_z[ch] : 0.f, bx = (live && bias_x) ? bias_x[ch] : 0.f;
     float A = 1.f, B = 0.f;
     if (live) {
-        for (int t = t0; t < t1; ++t) {
+        // the loads and gates of a row do not depend on the row before: eight rows at a time, so that their
+        // round trips to memory overlap, then the eight steps of the recurrence in order
+        int t = t0;
+        for (; t + 8 <= t1; t += 8) {
+            float zs[8], cs[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const T* row = proj + (size_t)(start + t + k) * proj_stride;
+                zs[k] = tw_to_float(row[ch]);
+                cs[k] = tw_to_float(row[width + ch]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float z = tw_sigmoidf(zs[k] + bz);
+                const float u = cs[k] + bx;
+                const float c = u >= 0.f ? u + 0.5f : tw_sigmoidf(u);
+                A *= 1.0f - z;
+                B = (1.0f - z) * B + z * c;
+            }
+        }
+        for (; t < t1; ++t) {
             const T* row = proj + (size_t)(start + t) * proj_stride;
             const float z = tw_sigmoidf(tw_to_float(row[ch]) + bz);
             const float u = tw_to_float(row[width + ch]) + bx;
@@ -95,7 +115,26 @@ mingru_scan_segments_kernel(T* __restrict__ out, int out_stride, const T* __rest
     __syncthreads();
     if (!live) return;
     float S = sA[seg][lane];
-    for (int t = t0; t < t1; ++t) {
+    int t = t0;
+    for (; t + 8 <= t1; t += 8) {
+        float zs[8], cs[8], gs[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const T* row = proj + (size_t)(start + t + k) * proj_stride;
+            zs[k] = tw_to_float(row[ch]);
+            cs[k] = tw_to_float(row[width + ch]);
+            gs[k] = tw_to_float(row[2 * width + ch]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float z = tw_sigmoidf(zs[k] + bz);
+            const float u = cs[k] + bx;
+            const float c = u >= 0.f ? u + 0.5f : tw_sigmoidf(u);
+            S = (1.0f - z) * S + z * c;
+            out[(size_t)(start + t + k) * out_stride + ch] = tw_from_float<T>(S * (gs[k] * tw_sigmoidf(gs[k])));
+        }
+    }
+    for (; t < t1; ++t) {
         const T* row = proj + (size_t)(start + t) * proj_stride;
         const float z = tw_sigmoidf(tw_to_float(row[ch]) + bz);
         const float u = tw_to_float(row[width + ch]) + bx;

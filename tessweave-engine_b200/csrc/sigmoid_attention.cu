@@ -37,21 +37,29 @@ sigattn_prepare_kernel(const T* __restrict__ proj, int proj_stride, const float*
                        const int* __restrict__ seq_slot, const int* __restrict__ block_table, int table_stride,
                        T* __restrict__ qf, T* __restrict__ k_cache, T* __restrict__ v_cache, int Hq, int Hkv, int D,
                        int page_size, int num_pages, int write_cache, int* status) {
-    extern __shared__ float smem[];          // q: Hq * D, k: Hkv * D, then 33 floats for the reductions
+    // q: Hq * D, k: Hkv * D, cos and sin: rot_dims / 2 each, the mixing matrix: Hq * Hq, then 33 floats for the reductions
+    extern __shared__ float smem[];
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int n = blockIdx.x;
     const int s = seq_of_token[n];
     if (s < 0) return;                       // padding row of a fixed-size batch
+    // With few rows the heads of a token are shared out over gridDim.y blocks: each block forms the norms (it needs
+    // the whole rows for them) and the rotation, folds the queries of its own heads, and block 0 writes the cache.
+    const int part = blockIdx.y, parts = gridDim.y;
     const int pos = positions[n];
     const int QW = Hq * D, KW = Hkv * D;
+    const int half = rot_dims >> 1;
     float* sq = smem;
-    float* sk = smem + QW;
-    float* scratch = sk + KW;
+    float* sk = sq + QW;
+    float* s_cos = sk + KW;
+    float* s_sin = s_cos + half;
+    float* s_mix = s_sin + half;
+    float* scratch = s_mix + (mix ? Hq * Hq : 0);
     const T* row = proj + (size_t)n * proj_stride;
 
     int page = -1;
-    if (write_cache) {
+    if (write_cache && part == 0) {
         const int blk = pos / page_size;
         page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
         if (page < 0 || page >= num_pages) {
@@ -60,7 +68,13 @@ sigattn_prepare_kernel(const T* __restrict__ proj, int proj_stride, const float*
         }
     }
     const int in_page = pos % page_size;
-
+    // the angles depend on the position and the pair only: each is evaluated once per block, not once per head
+    if (inv_freq) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &s_sin[i], &s_cos[i]);
+    }
+    if (mix) {
+        for (int i = threadIdx.x; i < Hq * Hq; i += blockDim.x) s_mix[i] = mix[i];
+    }
     float ssq = 0.f, ssk = 0.f;
     for (int i = threadIdx.x; i < QW; i += blockDim.x) {
         const float v = tw_to_float(row[i]);
@@ -84,15 +98,13 @@ sigattn_prepare_kernel(const T* __restrict__ proj, int proj_stride, const float*
     for (int i = threadIdx.x; i < QW; i += blockDim.x) sq[i] = (sq[i] * inv_q) * q_norm_w[i];
     for (int i = threadIdx.x; i < KW; i += blockDim.x) sk[i] = (sk[i] * inv_k) * k_norm_w[i];
     __syncthreads();
-    if (inv_freq && rot_dims > 1) {
-        const int half = rot_dims >> 1;
+    if (inv_freq && half > 0) {
         const int pairs = (Hq + Hkv) * half;
         for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
             const int head = idx / half, i = idx - head * half;
             float* base = (head < Hq ? sq + head * D : sk + (head - Hq) * D);
             const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float sn = s_sin[i], cs = s_cos[i];
             const float u = base[a], v = base[b];
             base[a] = u * cs - v * sn;
             base[b] = v * cs + u * sn;
@@ -106,17 +118,24 @@ sigattn_prepare_kernel(const T* __restrict__ proj, int proj_stride, const float*
         }
     }
     const int group = Hq / Hkv;
+    const int h_per = (Hq + parts - 1) / parts;
+    const int h_lo = part * h_per, h_hi = min(Hq, h_lo + h_per);
     T* out = qf + (size_t)n * Hq * KW;
-    for (int idx = threadIdx.x; idx < Hq * KW; idx += blockDim.x) {
-        const int h = idx / KW, rem = idx - h * KW;
+    // a thread owns columns (c, d) of the folded rows and walks the block's heads: the column's place is worked
+    // out once, and the inner loops have no division
+    for (int rem = threadIdx.x; rem < KW; rem += blockDim.x) {
         const int c = rem / D, d = rem - c * D;
-        float acc = 0.f;
-        if (mix) {
-            for (int g = c * group; g < (c + 1) * group; ++g) acc += mix[h * Hq + g] * sq[g * D + d];
-        } else if (h / group == c) {
-            acc = sq[h * D + d];
+        const float* q = sq + (c * group) * D + d;
+        for (int h = h_lo; h < h_hi; ++h) {
+            float acc = 0.f;
+            if (mix) {
+                const float* m = s_mix + h * Hq + c * group;
+                for (int g = 0; g < group; ++g) acc += m[g] * q[g * D];
+            } else if (h / group == c) {
+                acc = sq[h * D + d];
+            }
+            out[(size_t)h * KW + rem] = tw_from_float<T>(acc * scale);
         }
-        out[idx] = tw_from_float<T>(acc * scale);
     }
 }
 
@@ -128,20 +147,25 @@ TW_EXPORT int tw_sigattn_prepare(const void* proj, int proj_stride, const float*
                                  int dtype, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (D <= 0 || Hkv <= 0 || Hq % Hkv || rot_dims < 0 || rot_dims > D || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
-    const size_t smem = ((size_t)(Hq + Hkv) * D + 33) * sizeof(float);
+    if (!inv_freq) rot_dims = 0;
+    const size_t smem = ((size_t)(Hq + Hkv) * D + rot_dims + (mix ? (size_t)Hq * Hq : 0) + 33) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    // few rows: up to eight blocks per token, so that a decode step does not leave this to a handful of SMs
+    int parts = 1;
+    if (n_tokens < 148) parts = Hq < 8 ? Hq : 8;
+    const dim3 grid(n_tokens, parts);
     cudaError_t e;
     if (dtype == TW_F32) {
         e = cudaFuncSetAttribute(sigattn_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        return tw_launch(sigattn_prepare_kernel<float>, dim3(n_tokens), dim3(TW_SIG_PREP_THREADS), smem, stream, 1,
+        return tw_launch(sigattn_prepare_kernel<float>, grid, dim3(TW_SIG_PREP_THREADS), smem, stream, 1,
                          (const float*)proj, proj_stride, q_norm_w, k_norm_w, eps, mix, scale, inv_freq, rot_dims,
                          interleaved, positions, seq_of_token, seq_slot, block_table, table_stride, (float*)qf,
                          (float*)k_cache, (float*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache, status);
     }
     e = cudaFuncSetAttribute(sigattn_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return tw_launch(sigattn_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(TW_SIG_PREP_THREADS), smem, stream, 1,
+    return tw_launch(sigattn_prepare_kernel<__nv_bfloat16>, grid, dim3(TW_SIG_PREP_THREADS), smem, stream, 1,
                      (const __nv_bfloat16*)proj, proj_stride, q_norm_w, k_norm_w, eps, mix, scale, inv_freq, rot_dims,
                      interleaved, positions, seq_of_token, seq_slot, block_table, table_stride, (__nv_bfloat16*)qf,
                      (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,

@@ -38,29 +38,49 @@ static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple 
 
 __device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
-// 64 keys (j0 .. j0 + 63) of key/value head c into one stage; keys outside [j_lo, j_hi) become zero rows.
-__device__ __forceinline__ void load_chunk(bf16* dst, const bf16* __restrict__ cache, const int* __restrict__ table,
-                                           int table_stride, int j0, int j_lo, int j_hi, int c, int G, int P,
-                                           int num_pages, int* status) {
-    constexpr int CPR = D / 8;              // 16-byte pieces per row
-    for (int i = threadIdx.x; i < BN * CPR; i += blockDim.x) {
-        const int r = i / CPR, piece = i - r * CPR;
-        const int j = j0 + r;
-        const bf16* src = cache;
-        int bytes = 0;
-        if (j >= j_lo && j < j_hi) {
-            const int blk = j / P;
-            const int page = blk < table_stride ? table[blk] : -1;
-            if (page < 0 || page >= num_pages) {
-                if (piece == 0) atomicOr(status, TW_ERR_PAGE);
-            } else {
-                src = cache + (((size_t)page * G + c) * P + (j - blk * P)) * D + piece * 8;
-                bytes = 16;
+// Where the 16-byte pieces a thread copies for a tile of 64 keys come from: the page and the place inside it
+// are the same for every key/value head and for keys and values, so they are looked up once per tile and a chunk
+// costs a thread a few additions per piece.  Keys outside [j_lo, j_hi) get -1: their rows are zero-filled.
+template <int NT_THREADS>
+struct TileRows {
+    static constexpr int CPR = D / 8;                                   // 16-byte pieces per row
+    static constexpr int NI = (BN * CPR + NT_THREADS - 1) / NT_THREADS; // pieces per thread
+    long long off[NI];
+
+    __device__ __forceinline__ void look_up(const int* __restrict__ table, int table_stride, int j0, int j_lo, int j_hi,
+                                            int G, int P, int num_pages, int* status) {
+#pragma unroll
+        for (int k = 0; k < NI; ++k) {
+            const int i = threadIdx.x + k * NT_THREADS;
+            const int r = i / CPR, piece = i - r * CPR;
+            const int j = j0 + r;
+            off[k] = -1;
+            if (i < BN * CPR && j >= j_lo && j < j_hi) {
+                const int blk = j / P;
+                const int page = blk < table_stride ? table[blk] : -1;
+                if (page < 0 || page >= num_pages) {
+                    if (piece == 0) atomicOr(status, TW_ERR_PAGE);
+                } else {
+                    off[k] = ((long long)page * G * P + (j - blk * P)) * D + piece * 8;
+                }
             }
         }
-        cp_async16(dst + r * KSTR + piece * 8, src, bytes);
     }
-}
+
+    // the chunk of key/value head c into one stage
+    __device__ __forceinline__ void load(bf16* dst, const bf16* __restrict__ cache, int c, int P) const {
+        const long long head = (long long)c * P * D;
+#pragma unroll
+        for (int k = 0; k < NI; ++k) {
+            const int i = threadIdx.x + k * NT_THREADS;
+            if (i < BN * CPR) {
+                const int r = i / CPR, piece = i - r * CPR;
+                const bool live = off[k] >= 0;
+                cp_async16(dst + r * KSTR + piece * 8, live ? cache + off[k] + head : cache, live ? 16 : 0);
+            }
+        }
+    }
+};
 
 // S[nt] += A(16 rows of q, columns c * D ..) . K(keys key0 + 8 nt ..)^T for NT tiles of eight keys (NT even).
 template <int NT>
@@ -140,12 +160,14 @@ sigattn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __res
     }
     const int per_tile = G + 1;
     const int nchunks = ntiles * per_tile;
+    TileRows<32 * WARPS> rows;
     auto issue = [&](int n) {
         if (n < nchunks) {
             const int t = n / per_tile, k = n - t * per_tile;
             bf16* dst = ring + (n % NSTAGE) * CHUNK;
-            if (k < G) load_chunk(dst, k_cache, table, table_stride, (t0 + t) * BN, j_lo, j_hi, k, G, P, num_pages, status);
-            else load_chunk(dst, v_cache, table, table_stride, (t0 + t) * BN, j_lo, j_hi, kvh, G, P, num_pages, status);
+            if (k == 0) rows.look_up(table, table_stride, (t0 + t) * BN, j_lo, j_hi, G, P, num_pages, status);
+            if (k < G) rows.load(dst, k_cache, k, P);
+            else rows.load(dst, v_cache, kvh, P);
         }
         cp_async_commit();
     };
@@ -219,6 +241,7 @@ sigattn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __res
 // ---------------------------------------------------------------------------------------
 // Single tokens, keys cut into slices.  partial: [request][slice][head][D] fp32.
 // ---------------------------------------------------------------------------------------
+template <int MT>        // tiles of 16 heads a block serves: all heads of a request up to 16 * MT, so the keys are read once
 __global__ void __launch_bounds__(THREADS)
 sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, const float* __restrict__ bias,
                       const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
@@ -226,6 +249,7 @@ sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, 
                       const int* __restrict__ block_table, int table_stride, const bf16* __restrict__ k_cache,
                       const bf16* __restrict__ v_cache, int H, int G, int P, int num_pages, int window, int nsplit,
                       int* status) {
+    constexpr int HB = 16 * MT;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     tw_grid_wait();
     tw_grid_launch_dependents();
@@ -240,15 +264,15 @@ sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, 
     const int* table = block_table + (size_t)seq_slot[s] * table_stride;
     const int KW = G * D, QSTR = KW + 8;
     const int group = H / G;
-    const int h0 = ht * 16, heads = min(16, H - h0);
-    const int c_lo = h0 / group, c_hi = (h0 + heads - 1) / group;       // key/value heads this tile's values come from
+    const int h0 = ht * HB, heads = min(HB, H - h0);
+    const int c_lo = h0 / group, c_hi = (h0 + heads - 1) / group;       // key/value heads this block's values come from
     const int nv = c_hi - c_lo + 1;
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);
-    bf16* ring = qs + 16 * QSTR;
+    bf16* ring = qs + HB * QSTR;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     {
         const int pieces = KW / 8;
-        for (int i = threadIdx.x; i < 16 * pieces; i += THREADS) {
+        for (int i = threadIdx.x; i < HB * pieces; i += THREADS) {
             const int r = i / pieces, piece = i - r * pieces;
             const bool live = r < heads;
             const bf16* src = live ? qf + ((size_t)row * H + h0 + r) * KW + piece * 8 : qf;
@@ -257,25 +281,36 @@ sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, 
     }
     const int per_tile = G + nv;
     const int nchunks = ntiles * per_tile;
+    TileRows<THREADS> rows;
     auto issue = [&](int n) {
         if (n < nchunks) {
             const int t = n / per_tile, k = n - t * per_tile;
             bf16* dst = ring + (n % NSTAGE) * CHUNK;
-            if (k < G) load_chunk(dst, k_cache, table, table_stride, (t_first + t) * BN, j_lo, j_hi, k, G, P, num_pages, status);
-            else load_chunk(dst, v_cache, table, table_stride, (t_first + t) * BN, j_lo, j_hi, c_lo + (k - G), G, P, num_pages, status);
+            if (k == 0) rows.look_up(table, table_stride, (t_first + t) * BN, j_lo, j_hi, G, P, num_pages, status);
+            if (k < G) rows.load(dst, k_cache, k, P);
+            else rows.load(dst, v_cache, c_lo + (k - G), P);
         }
         cp_async_commit();
     };
     issue(0);
     issue(1);
-    float S[2][4], O[D / 8][4];
+    float S[MT][2][4], O[MT][D / 8][4], w[MT][2][4];
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) { O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f; }
+    for (int m = 0; m < MT; ++m) {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { O[m][i][0] = O[m][i][1] = O[m][i][2] = O[m][i][3] = 0.f; }
+    }
     const int g = lane >> 2, tq = lane & 3;
-    const int head_a = h0 + g, head_b = h0 + g + 8;
-    const float b_a = (bias && head_a < H) ? bias[head_a] : 0.f, b_b = (bias && head_b < H) ? bias[head_b] : 0.f;
-    const int c_a = head_a / group, c_b = head_b / group;
-    float w[2][4];
+    float b_a[MT], b_b[MT];
+    int c_a[MT], c_b[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const int head_a = h0 + m * 16 + g, head_b = head_a + 8;
+        b_a[m] = (bias && head_a < H) ? bias[head_a] : 0.f;
+        b_b[m] = (bias && head_b < H) ? bias[head_b] : 0.f;
+        c_a[m] = head_a < H ? head_a / group : -1;
+        c_b[m] = head_b < H ? head_b / group : -1;
+    }
     for (int n = 0; n < nchunks; ++n) {
         issue(n + 2);
         cp_async_wait<2>();
@@ -283,49 +318,66 @@ sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, 
         const int t = n / per_tile, k = n - t * per_tile;
         const bf16* stage = ring + (n % NSTAGE) * CHUNK;
         if (k < G) {
-            if (k == 0) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i) { S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.f; }
+            for (int m = 0; m < MT; ++m) {
+                if (m * 16 >= heads) continue;
+                if (k == 0) {
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) { S[m][i][0] = S[m][i][1] = S[m][i][2] = S[m][i][3] = 0.f; }
+                }
+                scores_chunk<2>(S[m], qs, QSTR, m * 16, k, stage, warp * 16, lane);
             }
-            scores_chunk<2>(S, qs, QSTR, 0, k, stage, warp * 16, lane);
         } else {
-            if (k == G) {
-                const int jbase = (t_first + t) * BN + warp * 16;
+            const int c = c_lo + (k - G);
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
+            for (int m = 0; m < MT; ++m) {
+                if (m * 16 >= heads) continue;
+                if (k == G) {
+                    const int jbase = (t_first + t) * BN + warp * 16;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int je = jbase + nt * 8 + 2 * tq + (e & 1);
-                        const bool ok = je >= j_lo && je < j_hi && ((e & 2) ? head_b : head_a) < H;
-                        w[nt][e] = ok ? sigmoid_fast(S[nt][e] + ((e & 2) ? b_b : b_a)) : 0.f;
+                    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int je = jbase + nt * 8 + 2 * tq + (e & 1);
+                            const bool ok = je >= j_lo && je < j_hi && ((e & 2) ? c_b[m] : c_a[m]) >= 0;
+                            w[m][nt][e] = ok ? sigmoid_fast(S[m][nt][e] + ((e & 2) ? b_b[m] : b_a[m])) : 0.f;
+                        }
                     }
                 }
+                // does any head of this tile of sixteen take its values from key/value head c?
+                const int m_lo = (h0 + m * 16) / group, m_hi = (min(H, h0 + m * 16 + 16) - 1) / group;
+                if (c < m_lo || c > m_hi) continue;
+                const bool use_a = c_a[m] == c, use_b = c_b[m] == c;
+                uint32_t pa[4];
+                pa[0] = use_a ? pack_bf16(w[m][0][0], w[m][0][1]) : 0u;
+                pa[1] = use_b ? pack_bf16(w[m][0][2], w[m][0][3]) : 0u;
+                pa[2] = use_a ? pack_bf16(w[m][1][0], w[m][1][1]) : 0u;
+                pa[3] = use_b ? pack_bf16(w[m][1][2], w[m][1][3]) : 0u;
+                values_step(O[m], pa, stage, warp * 16, lane);
             }
-            const int c = c_lo + (k - G);
-            const bool use_a = c_a == c, use_b = c_b == c;
-            uint32_t pa[4];
-            pa[0] = use_a ? pack_bf16(w[0][0], w[0][1]) : 0u;
-            pa[1] = use_b ? pack_bf16(w[0][2], w[0][3]) : 0u;
-            pa[2] = use_a ? pack_bf16(w[1][0], w[1][1]) : 0u;
-            pa[3] = use_b ? pack_bf16(w[1][2], w[1][3]) : 0u;
-            values_step(O, pa, stage, warp * 16, lane);
         }
         __syncthreads();
     }
-    // the four warps' sums meet in shared memory (the ring is free now), in warp order
+    // the four warps' sums meet in shared memory (the ring is free now), in warp order, one tile of heads at a time
     cp_async_wait<0>();
     __syncthreads();
     float* sums = reinterpret_cast<float*>(ring);          // [4][16][D]
 #pragma unroll
-    for (int nd = 0; nd < D / 8; ++nd) {
-        const int col = nd * 8 + 2 * tq;
-        *reinterpret_cast<float2*>(sums + ((size_t)warp * 16 + g) * D + col) = make_float2(O[nd][0], O[nd][1]);
-        *reinterpret_cast<float2*>(sums + ((size_t)warp * 16 + g + 8) * D + col) = make_float2(O[nd][2], O[nd][3]);
-    }
-    __syncthreads();
-    float* dst = partial + (((size_t)s * nsplit + sp) * H + h0) * D;
-    for (int i = threadIdx.x; i < heads * D; i += THREADS) {
-        dst[i] = ((sums[i] + sums[16 * D + i]) + sums[2 * 16 * D + i]) + sums[3 * 16 * D + i];
+    for (int m = 0; m < MT; ++m) {
+        if (m * 16 >= heads) continue;
+#pragma unroll
+        for (int nd = 0; nd < D / 8; ++nd) {
+            const int col = nd * 8 + 2 * tq;
+            *reinterpret_cast<float2*>(sums + ((size_t)warp * 16 + g) * D + col) = make_float2(O[m][nd][0], O[m][nd][1]);
+            *reinterpret_cast<float2*>(sums + ((size_t)warp * 16 + g + 8) * D + col) = make_float2(O[m][nd][2], O[m][nd][3]);
+        }
+        __syncthreads();
+        const int live = min(16, heads - m * 16);
+        float* dst = partial + (((size_t)s * nsplit + sp) * H + h0 + m * 16) * D;
+        for (int i = threadIdx.x; i < live * D; i += THREADS) {
+            dst[i] = ((sums[i] + sums[16 * D + i]) + sums[2 * 16 * D + i]) + sums[3 * 16 * D + i];
+        }
+        __syncthreads();
     }
 }
 
@@ -356,9 +408,8 @@ TW_EXPORT int tw_sigattn_head_dim() { return D; }
 
 // Shared memory a launch needs, for the caller to decide whether the shape fits (227 KB per block).
 TW_EXPORT long tw_sigattn_prefill_smem(int G, int rows) { return (long)((size_t)rows * (G * D + 8) * sizeof(bf16) + ring_bytes()); }
-TW_EXPORT long tw_sigattn_decode_smem(int G) {
-    const size_t ring = ring_bytes() > (size_t)4 * 16 * D * sizeof(float) ? ring_bytes() : (size_t)4 * 16 * D * sizeof(float);
-    return (long)(16 * (G * D + 8) * sizeof(bf16) + ring);
+TW_EXPORT long tw_sigattn_decode_smem(int G, int heads_per_block) {
+    return (long)((size_t)heads_per_block * (G * D + 8) * sizeof(bf16) + ring_bytes());     // the ring also holds the warps' sums
 }
 
 TW_EXPORT int tw_sigattn_prefill(void* out, int out_stride, const void* qf, const float* bias, const void* gate,
@@ -390,12 +441,16 @@ TW_EXPORT int tw_sigattn_decode(void* out, int out_stride, float* partial, const
                                 int num_pages, int window, int nsplit, int* status, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (G <= 0 || H % G || nsplit <= 0) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)tw_sigattn_decode_smem(G);
+    // a block serves 32 heads where there are more than 16 (the keys are then read once for all of them)
+    const bool two = H > 16 && (size_t)tw_sigattn_decode_smem(G, 32) <= 227 * 1024;
+    const int hb = two ? 32 : 16;
+    const size_t smem = (size_t)tw_sigattn_decode_smem(G, hb);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(sigattn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    auto kernel = two ? sigattn_decode_kernel<2> : sigattn_decode_kernel<1>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const dim3 grid(nsplit, (H + 15) / 16, n_seqs);
-    int code = tw_launch(sigattn_decode_kernel, grid, dim3(THREADS), smem, stream, 1, partial, (const bf16*)qf, bias,
+    const dim3 grid(nsplit, (H + hb - 1) / hb, n_seqs);
+    int code = tw_launch(kernel, grid, dim3(THREADS), smem, stream, 1, partial, (const bf16*)qf, bias,
                          seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table, table_stride, (const bf16*)k_cache,
                          (const bf16*)v_cache, H, G, page_size, num_pages, window, nsplit, status);
     if (code != 0) return code;
