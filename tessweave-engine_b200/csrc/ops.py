@@ -268,6 +268,49 @@ def sigmoid_attention_prefill(out, qf, bias, gate, seq_q_start, seq_q_len, seq_k
     _check(code, "sigmoid_attention_prefill")
 
 
+SIGMOID_TCGEN05_MIN_TOKENS = 128
+
+
+def sigmoid_attention_tcgen05(dtype: torch.dtype, head_dim: int, n_kv_heads: int, page_size: int, max_q_len: int) -> bool:
+    """Whether a step whose longest portion has ``max_q_len`` tokens runs its sigmoid attention on the tcgen05 kernel
+    (csrc/sigmoid_attention_tcgen05.cu): bfloat16, head size 64 or 128, pages that divide a tile of 128 keys or are a
+    multiple of it, folded queries of 128 rows that leave room for three chunks of keys in shared memory, and a
+    portion of at least 128 tokens.  TESSWEAVE_SIGMOID_PREFILL=mma|tcgen05 forces one of the two (the latter only
+    for shapes the kernel takes)."""
+    import os
+    if dtype != torch.bfloat16 or head_dim not in (64, 128) or page_size < 4:
+        return False
+    if not (128 % page_size == 0 or page_size % 128 == 0):
+        return False
+    chunk = (head_dim // 64) * 16384
+    if (227 * 1024 - 1024 - 512 - n_kv_heads * chunk) // chunk < 3:
+        return False
+    forced = os.environ.get("TESSWEAVE_SIGMOID_PREFILL")
+    if forced == "mma":
+        return False
+    if forced == "tcgen05":
+        return True
+    return max_q_len >= SIGMOID_TCGEN05_MIN_TOKENS
+
+
+def sigmoid_attention_prefill_tcgen05(out, qf, bias, gate, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
+                                      k_pages, v_pages, n_seqs: int, max_q_len: int, n_q_heads: int, n_kv_heads: int,
+                                      head_dim: int, window: int, skip_singles: bool, status: torch.Tensor) -> None:
+    """The same as ``sigmoid_attention_prefill`` on the 5th-generation tensor cores (TMA, tcgen05.mma, S and O in
+    tensor memory), for the shapes ``sigmoid_attention_tcgen05`` names."""
+    _sigattn_checks(out, qf, bias, gate, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim)
+    _need(out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0, "tcgen05 sigmoid attention: rows of out must be 16-byte aligned")
+    _need(gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0),
+          "tcgen05 sigmoid attention: rows of the gate must be 16-byte aligned")
+    code = _fn("sigmoid_attention_tcgen05", "tw_sigattn_prefill_tc5", {"TW_HEAD_DIM": head_dim})(
+        _ptr(out), c_int(out.stride(0)), _ptr(qf), _ptr(bias), _ptr(gate), c_int(0 if gate is None else gate.stride(0)),
+        _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table),
+        c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_seqs), c_int(max_q_len), c_int(n_q_heads),
+        c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), c_int(window), c_int(1 if skip_singles else 0),
+        _ptr(status), _stream())
+    _check(code, "sigmoid_attention_prefill_tcgen05")
+
+
 def sigmoid_attention_decode(out, partial, qf, bias, gate, seq_q_start, seq_q_len, seq_kv_len, seq_slot, block_table,
                              k_pages, v_pages, n_seqs: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int,
                              nsplit: int, status: torch.Tensor) -> None:

@@ -119,7 +119,13 @@ class SigmoidAttention(Mixer):
         # read the same flat batch and skip the other's requests
         singles = ctx.decode_only or ctx.fixed_shape or any(count == 1 for count in ctx.host_q_len)
         if not ctx.decode_only:
-            ops.sigmoid_attention_prefill(out, qf, self.bias, gate, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
+            # long portions: tcgen05 kernel (TMA, S and O in tensor memory); short ones, and the shapes it does not
+            # take, stay on the mma.sync kernel, which starts faster
+            prefill = ops.sigmoid_attention_prefill
+            if ops.sigmoid_attention_tcgen05(self.runtime.dtype, self.head_dim, self.n_kv_heads, cache.k_pages.shape[2],
+                                             ctx.max_q_len):
+                prefill = ops.sigmoid_attention_prefill_tcgen05
+            prefill(out, qf, self.bias, gate, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len,
                                           ctx.seq_slot, cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs,
                                           ctx.max_q_len, self.n_heads, self.n_kv_heads, self.head_dim, window, singles,
                                           ctx.status)

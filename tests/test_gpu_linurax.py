@@ -179,12 +179,18 @@ def test_sigmoid_attention_alone(dtype, shape):
     close(got_a1, want_a[13:], dtype, "a's second portion")
 
 
-@pytest.mark.parametrize("heads,kv,d,window", [(8, 2, 64, None), (20, 4, 32, None), (3, 1, 96, None), (4, 4, 128, 150), (2, 1, 16, 65)])
-def test_tensor_core_attention_against_the_exact_kernel(heads, kv, d, window, monkeypatch):
+@pytest.mark.parametrize("prefill", ["mma", "tcgen05"])
+@pytest.mark.parametrize("heads,kv,d,window", [(8, 2, 64, None), (20, 4, 32, None), (3, 1, 96, None), (4, 4, 128, 150), (2, 1, 16, 65),
+                                               (28, 4, 128, None), (6, 3, 64, 300)])
+def test_tensor_core_attention_against_the_exact_kernel(heads, kv, d, window, prefill, monkeypatch):
     """bfloat16, several hundred keys: portions whose tiles end inside pages and inside tiles of 64 keys, and
     single tokens whose keys are cut into slices, through the tensor-core kernels and through the exact kernel
-    (same rounded inputs, so they differ by the rounding of the weights to bfloat16 and no more)."""
+    (same rounded inputs, so they differ by the rounding of the weights to bfloat16 and no more).  Portions run
+    on the mma.sync kernel and on the tcgen05 kernel."""
     hidden, page = 64, 16
+    if prefill == "tcgen05" and d not in (64, 128):
+        pytest.skip("the tcgen05 kernel is built for head sizes 64 and 128")
+    monkeypatch.setenv("TESSWEAVE_SIGMOID_PREFILL", prefill)     # tcgen05: every portion, also the short ones
     rt = Runtime(torch.device("cuda"), torch.bfloat16)
     spec = PartSpec("sigmoid_attention", {"hidden": hidden, "n_heads": heads, "n_kv_heads": kv, "head_dim": d,
                                           "scale": 1.2 / d ** 0.5, "eps": 1e-5, "window": window,
