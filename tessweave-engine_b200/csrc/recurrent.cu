@@ -12,6 +12,11 @@
 #define TW_SCAN_THREADS 128
 
 __device__ __forceinline__ float tw_sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+// the segmented kernel's gates: accurate in float32 runs; in bfloat16 runs, whose pre-activations carry 8 bits,
+// the hardware's exponential and reciprocal (fp32 all the same, a few units in the last place)
+template <typename T> __device__ __forceinline__ float tw_gate_sigmoid(float x);
+template <> __device__ __forceinline__ float tw_gate_sigmoid<float>(float x) { return 1.0f / (1.0f + expf(-x)); }
+template <> __device__ __forceinline__ float tw_gate_sigmoid<__nv_bfloat16>(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 // Short portions and single tokens: one thread per (request, channel) walks the request's rows of this step in order.
 template <typename T>
@@ -83,18 +88,18 @@ mingru_scan_segments_kernel(T* __restrict__ out, int out_stride, const T* __rest
             }
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                const float z = tw_sigmoidf(zs[k] + bz);
+                const float z = tw_gate_sigmoid<T>(zs[k] + bz);
                 const float u = cs[k] + bx;
-                const float c = u >= 0.f ? u + 0.5f : tw_sigmoidf(u);
+                const float c = u >= 0.f ? u + 0.5f : tw_gate_sigmoid<T>(u);
                 A *= 1.0f - z;
                 B = (1.0f - z) * B + z * c;
             }
         }
         for (; t < t1; ++t) {
             const T* row = proj + (size_t)(start + t) * proj_stride;
-            const float z = tw_sigmoidf(tw_to_float(row[ch]) + bz);
+            const float z = tw_gate_sigmoid<T>(tw_to_float(row[ch]) + bz);
             const float u = tw_to_float(row[width + ch]) + bx;
-            const float c = u >= 0.f ? u + 0.5f : tw_sigmoidf(u);
+            const float c = u >= 0.f ? u + 0.5f : tw_gate_sigmoid<T>(u);
             A *= 1.0f - z;
             B = (1.0f - z) * B + z * c;
         }
@@ -127,21 +132,21 @@ mingru_scan_segments_kernel(T* __restrict__ out, int out_stride, const T* __rest
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const float z = tw_sigmoidf(zs[k] + bz);
+            const float z = tw_gate_sigmoid<T>(zs[k] + bz);
             const float u = cs[k] + bx;
-            const float c = u >= 0.f ? u + 0.5f : tw_sigmoidf(u);
+            const float c = u >= 0.f ? u + 0.5f : tw_gate_sigmoid<T>(u);
             S = (1.0f - z) * S + z * c;
-            out[(size_t)(start + t + k) * out_stride + ch] = tw_from_float<T>(S * (gs[k] * tw_sigmoidf(gs[k])));
+            out[(size_t)(start + t + k) * out_stride + ch] = tw_from_float<T>(S * (gs[k] * tw_gate_sigmoid<T>(gs[k])));
         }
     }
     for (; t < t1; ++t) {
         const T* row = proj + (size_t)(start + t) * proj_stride;
-        const float z = tw_sigmoidf(tw_to_float(row[ch]) + bz);
+        const float z = tw_gate_sigmoid<T>(tw_to_float(row[ch]) + bz);
         const float u = tw_to_float(row[width + ch]) + bx;
         const float g = tw_to_float(row[2 * width + ch]);
-        const float c = u >= 0.f ? u + 0.5f : tw_sigmoidf(u);
+        const float c = u >= 0.f ? u + 0.5f : tw_gate_sigmoid<T>(u);
         S = (1.0f - z) * S + z * c;
-        out[(size_t)(start + t) * out_stride + ch] = tw_from_float<T>(S * (g * tw_sigmoidf(g)));
+        out[(size_t)(start + t) * out_stride + ch] = tw_from_float<T>(S * (g * tw_gate_sigmoid<T>(g)));
     }
 }
 

@@ -121,8 +121,42 @@ sigattn_prepare_kernel(const T* __restrict__ proj, int proj_stride, const float*
     const int h_per = (Hq + parts - 1) / parts;
     const int h_lo = part * h_per, h_hi = min(Hq, h_lo + h_per);
     T* out = qf + (size_t)n * Hq * KW;
-    // a thread owns columns (c, d) of the folded rows and walks the block's heads: the column's place is worked
-    // out once, and the inner loops have no division
+    if (mix && (D & 3) == 0) {
+        // a thread owns four neighbouring columns (c, d .. d + 3) of the folded rows and eight heads at a time: one
+        // 16-byte read of q per head of the group, one broadcast read of the mixing matrix per four products
+        for (int rem4 = threadIdx.x; rem4 < (KW >> 2); rem4 += blockDim.x) {
+            const int rem = rem4 << 2;
+            const int c = rem / D, d = rem - c * D;
+            const float* q = sq + (c * group) * D + d;
+            for (int hb = h_lo; hb < h_hi; hb += 8) {
+                float4 acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int g = 0; g < group; ++g) {
+                    const float4 qv = *reinterpret_cast<const float4*>(q + g * D);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (hb + j < h_hi) {
+                            const float m = s_mix[(hb + j) * Hq + c * group + g];
+                            acc[j].x += m * qv.x; acc[j].y += m * qv.y; acc[j].z += m * qv.z; acc[j].w += m * qv.w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (hb + j < h_hi) {
+                        T* dst = out + (size_t)(hb + j) * KW + rem;
+                        dst[0] = tw_from_float<T>(acc[j].x * scale);
+                        dst[1] = tw_from_float<T>(acc[j].y * scale);
+                        dst[2] = tw_from_float<T>(acc[j].z * scale);
+                        dst[3] = tw_from_float<T>(acc[j].w * scale);
+                    }
+                }
+            }
+        }
+        return;
+    }
+    // any head size, or no mixing: a thread owns columns (c, d) of the folded rows and walks the block's heads
     for (int rem = threadIdx.x; rem < KW; rem += blockDim.x) {
         const int c = rem / D, d = rem - c * D;
         const float* q = sq + (c * group) * D + d;

@@ -97,3 +97,46 @@ def test_generate_as_a_user_starts_it(name, tmp_path):
     assert replayed.returncode == 0 and {json.loads(l)["event"] for l in replayed.stdout.splitlines()} <= \
         {"step", "admit", "finish", "first_token", "fatal"}
     assert sum(json.loads(l)["event"] == "step" for l in replayed.stdout.splitlines()) >= 3 + 7     # 9 prompt tokens in portions of 4, then 7 single tokens
+
+
+# ---------------------------------------------------------------------------
+# the Linurax decoder through the same command line
+# ---------------------------------------------------------------------------
+def test_doctor_and_inspect_know_linurax(tmp_path):
+    from tiny_linurax import LINURAX_A
+    assert "Linurax" in json.loads(run_cli("doctor").stdout)["architectures"]
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(LINURAX_A))
+    folder = tmp_path / "model"
+    assert run_cli("init", folder, "--config", config, "--seed", 2, "--init-std", 0.1).returncode == 0
+    proc = run_cli("inspect", folder, "--kv-blocks", 10, "--block-size", 8)
+    assert proc.returncode == 0, proc.stderr
+    out = json.loads(proc.stdout)
+    attention = [l["mixer"] for l in LINURAX_A["layers"] if l["type"] == "attention"]
+    per_token = sum(2 * m["kv_heads"] * m["dim"] for m in attention)          # the key and the raw key kept as the value
+    assert out["kv_bf16_bytes"] == per_token * 2 * 10 * 8 and out["layers_in_schedule"] == len(LINURAX_A["layers"])
+    assert out["state_bytes_per_request"] == 4 * sum(l["mixer"]["width"] for l in LINURAX_A["layers"] if l["type"] == "mingru")
+    assert out["architecture"]["width"] == LINURAX_A["width"]
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps({**LINURAX_A, "layers": [{**LINURAX_A["layers"][0], "type": "conv"}]}))
+    proc = run_cli("inspect", bad)
+    assert proc.returncode != 0 and "not implemented" in proc.stderr
+
+
+@pytest.mark.gpu
+def test_generate_linurax_as_a_user_starts_it(tmp_path):
+    """init -> generate --prompt-ids in float32 -> the plain implementation's greedy continuation."""
+    import plain_linurax
+    from tiny_linurax import LINURAX_B
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(LINURAX_B))
+    folder = tmp_path / "model"
+    assert run_cli("init", folder, "--config", config, "--seed", 11, "--init-std", 0.2).returncode == 0
+    prompt = [5, 17, 3, 20, 41, 7, 96, 10, 23]
+    proc = run_cli("generate", folder, "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32", "--max-tokens", 8,
+                   "--ignore-eos", "--log", tmp_path / "runs" / "engine.jsonl", "--block-size", 8, "--kv-blocks", 32,
+                   "--prefill-chunk", 4, "--max-context", 256)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    got = [int(t) for t in proc.stdout.strip().split(",")]
+    assert got == plain_linurax.greedy(folder, prompt, 8)
