@@ -38,7 +38,7 @@ sigattn_prepare_kernel(const T* __restrict__ proj, int proj_stride, const float*
                        T* __restrict__ qf, T* __restrict__ k_cache, T* __restrict__ v_cache, int Hq, int Hkv, int D,
                        int page_size, int num_pages, int write_cache, int* status) {
     // q: Hq * D, k: Hkv * D, cos and sin: rot_dims / 2 each, the mixing matrix: Hq * Hq, then 33 floats for the reductions
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int n = blockIdx.x;
@@ -173,6 +173,165 @@ sigattn_prepare_kernel(const T* __restrict__ proj, int proj_stride, const float*
     }
 }
 
+// The same for bfloat16 rows whose head size is a multiple of 8 and whose rotation pairs neighbours (or is absent):
+// eight values per access.  A thread that normalises a piece also rotates it (both values of a pair are its own),
+// and a piece of k goes from registers straight to its page.
+__device__ __forceinline__ void tw_unpack8(const uint4& raw, float (&x)[8]) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        x[2 * e] = f.x;
+        x[2 * e + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 tw_pack8(const float (&x)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+    return raw;
+}
+
+__global__ void __launch_bounds__(TW_SIG_PREP_THREADS)
+sigattn_prepare_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj, int proj_stride, const float* __restrict__ q_norm_w,
+                              const float* __restrict__ k_norm_w, float eps, const float* __restrict__ mix, float scale,
+                              const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ positions,
+                              const int* __restrict__ seq_of_token, const int* __restrict__ seq_slot,
+                              const int* __restrict__ block_table, int table_stride, __nv_bfloat16* __restrict__ qf,
+                              __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int Hq, int Hkv, int D,
+                              int page_size, int num_pages, int write_cache, int* status) {
+    extern __shared__ __align__(16) float smem[];
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int n = blockIdx.x;
+    const int s = seq_of_token[n];
+    if (s < 0) return;
+    const int part = blockIdx.y, parts = gridDim.y;
+    const int pos = positions[n];
+    const int QW = Hq * D, KW = Hkv * D;
+    const int half = rot_dims >> 1;
+    float* sq = smem;
+    float* sk = sq + QW;
+    float* s_cos = sk + KW;
+    float* s_sin = s_cos + half;
+    float* s_mix = s_sin + half;
+    float* scratch = s_mix + (mix ? Hq * Hq : 0);
+    const uint4* row = reinterpret_cast<const uint4*>(proj + (size_t)n * proj_stride);
+    int page = -1;
+    if (write_cache && part == 0) {
+        const int blk = pos / page_size;
+        page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(status, TW_ERR_PAGE);
+            page = -1;
+        }
+    }
+    const int in_page = pos % page_size;
+    if (inv_freq) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &s_sin[i], &s_cos[i]);
+    }
+    if (mix) {
+        for (int i = threadIdx.x; i < Hq * Hq; i += blockDim.x) s_mix[i] = mix[i];
+    }
+    const int q8 = QW >> 3, all8 = (QW + KW) >> 3;
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = threadIdx.x; i < all8; i += blockDim.x) {
+        const uint4 raw = row[i];
+        float x[8];
+        tw_unpack8(raw, x);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+        float* dst = i < q8 ? sq + 8 * i : sk + 8 * (i - q8);
+        *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(x[4], x[5], x[6], x[7]);
+        if (i < q8) {
+            ssq += ss;
+        } else {
+            ssk += ss;
+            if (page >= 0) {                 // the value is the key as projected
+                const int col = 8 * (i - q8), c = col / D, d = col - c * D;
+                *reinterpret_cast<uint4*>(v_cache + (((size_t)page * Hkv + c) * page_size + in_page) * D + d) = raw;
+            }
+        }
+    }
+    ssq = tw_block_sum(ssq, scratch);
+    ssk = tw_block_sum(ssk, scratch);
+    const float inv_q = 1.0f / sqrtf(ssq / (float)QW + eps);
+    const float inv_k = 1.0f / sqrtf(ssk / (float)KW + eps);
+    for (int i = threadIdx.x; i < all8; i += blockDim.x) {
+        const bool is_q = i < q8;
+        const int col = is_q ? 8 * i : 8 * (i - q8);
+        float* src = (is_q ? sq : sk) + col;
+        const float* wsrc = (is_q ? q_norm_w : k_norm_w) + col;
+        const float inv = is_q ? inv_q : inv_k;
+        if (!is_q && page < 0) continue;     // nobody reads this block's k
+        const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+        const float4 wa = *reinterpret_cast<const float4*>(wsrc), wb = *reinterpret_cast<const float4*>(wsrc + 4);
+        float x[8] = {(a.x * inv) * wa.x, (a.y * inv) * wa.y, (a.z * inv) * wa.z, (a.w * inv) * wa.w,
+                      (b.x * inv) * wb.x, (b.y * inv) * wb.y, (b.z * inv) * wb.z, (b.w * inv) * wb.w};
+        const int head = col / D, d0 = col - head * D;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int pi = (d0 >> 1) + j;
+            if (pi < half) {
+                const float sn = s_sin[pi], cs = s_cos[pi];
+                const float u = x[2 * j], v = x[2 * j + 1];
+                x[2 * j] = u * cs - v * sn;
+                x[2 * j + 1] = v * cs + u * sn;
+            }
+        }
+        if (is_q) {
+            *reinterpret_cast<float4*>(src) = make_float4(x[0], x[1], x[2], x[3]);
+            *reinterpret_cast<float4*>(src + 4) = make_float4(x[4], x[5], x[6], x[7]);
+        } else {
+            *reinterpret_cast<uint4*>(k_cache + (((size_t)page * Hkv + head) * page_size + in_page) * D + d0) = tw_pack8(x);
+        }
+    }
+    __syncthreads();
+    const int group = Hq / Hkv;
+    const int h_per = (Hq + parts - 1) / parts;
+    const int h_lo = part * h_per, h_hi = min(Hq, h_lo + h_per);
+    __nv_bfloat16* out = qf + (size_t)n * Hq * KW;
+    for (int rem4 = threadIdx.x; rem4 < (KW >> 2); rem4 += blockDim.x) {
+        const int rem = rem4 << 2;
+        const int c = rem / D, d = rem - c * D;
+        const float* q = sq + (c * group) * D + d;
+        for (int hb = h_lo; hb < h_hi; hb += 8) {
+            float4 acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (mix) {
+                for (int g = 0; g < group; ++g) {
+                    const float4 qv = *reinterpret_cast<const float4*>(q + g * D);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (hb + j < h_hi) {
+                            const float m = s_mix[(hb + j) * Hq + c * group + g];
+                            acc[j].x += m * qv.x; acc[j].y += m * qv.y; acc[j].z += m * qv.z; acc[j].w += m * qv.w;
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (hb + j < h_hi && (hb + j) / group == c) acc[j] = *reinterpret_cast<const float4*>(sq + (hb + j) * D + d);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (hb + j < h_hi) {
+                    uint2 w;
+                    *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(acc[j].x * scale, acc[j].y * scale);
+                    *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(acc[j].z * scale, acc[j].w * scale);
+                    *reinterpret_cast<uint2*>(out + (size_t)(hb + j) * KW + rem) = w;
+                }
+            }
+        }
+    }
+}
+
 TW_EXPORT int tw_sigattn_prepare(const void* proj, int proj_stride, const float* q_norm_w, const float* k_norm_w,
                                  float eps, const float* mix, float scale, const float* inv_freq, int rot_dims,
                                  int interleaved, const int* positions, const int* seq_of_token, const int* seq_slot,
@@ -196,6 +355,18 @@ TW_EXPORT int tw_sigattn_prepare(const void* proj, int proj_stride, const float*
                          (const float*)proj, proj_stride, q_norm_w, k_norm_w, eps, mix, scale, inv_freq, rot_dims,
                          interleaved, positions, seq_of_token, seq_slot, block_table, table_stride, (float*)qf,
                          (float*)k_cache, (float*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache, status);
+    }
+    const bool aligned = !((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(qf) | reinterpret_cast<uintptr_t>(k_cache) |
+                            reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(q_norm_w) |
+                            reinterpret_cast<uintptr_t>(k_norm_w)) & 15);
+    if ((D & 7) == 0 && (proj_stride & 7) == 0 && aligned && (interleaved || !inv_freq)) {
+        e = cudaFuncSetAttribute(sigattn_prepare_bf16x8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        return tw_launch(sigattn_prepare_bf16x8_kernel, grid, dim3(TW_SIG_PREP_THREADS), smem, stream, 1,
+                         (const __nv_bfloat16*)proj, proj_stride, q_norm_w, k_norm_w, eps, mix, scale, inv_freq, rot_dims,
+                         positions, seq_of_token, seq_slot, block_table, table_stride, (__nv_bfloat16*)qf,
+                         (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, Hq, Hkv, D, page_size, num_pages, write_cache,
+                         status);
     }
     e = cudaFuncSetAttribute(sigattn_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
