@@ -215,14 +215,14 @@ def sigmoid_attention_generic(out: torch.Tensor, qf: torch.Tensor, bias: torch.T
 
 def sigmoid_attention_tensor_cores(dtype: torch.dtype, head_dim: int, n_kv_heads: int) -> bool:
     """Whether the tensor-core kernels (csrc/sigmoid_attention_bf16.cu) take the shape: bfloat16, a head size that is a
-    multiple of 16 up to 256, and a tile of 64 folded queries plus the ring of key chunks within 227 KB of shared
+    multiple of 16 up to 256, and a tile of 64 folded queries plus the ring of four key chunks within 227 KB of shared
     memory.  TESSWEAVE_SIGMOID_ATTENTION=exact sends everything to the exact kernel."""
     import os
     if os.environ.get("TESSWEAVE_SIGMOID_ATTENTION") == "exact":
         return False
     if dtype != torch.bfloat16 or head_dim % 16 or not 16 <= head_dim <= 256:
         return False
-    return 64 * (n_kv_heads * head_dim + 8) * 2 + 3 * 64 * (head_dim + 8) * 2 <= 227 * 1024
+    return 64 * (n_kv_heads * head_dim + 8) * 2 + 4 * 64 * (head_dim + 8) * 2 <= 227 * 1024
 
 
 def sigmoid_decode_splits(n_seqs: int, n_heads: int, max_kv_len: int) -> int:
@@ -271,19 +271,28 @@ def sigmoid_attention_prefill(out, qf, bias, gate, seq_q_start, seq_q_len, seq_k
 SIGMOID_TCGEN05_MIN_TOKENS = 128
 
 
+def sigmoid_tcgen05_key_tile() -> int:
+    """Keys per tile of the tcgen05 sigmoid attention: 128, or 64 with TESSWEAVE_SIGMOID_KEY_TILE=64 (chunks of 64
+    keys make the rings beside the folded queries twice as deep, but a tile's fixed costs come twice as often:
+    measured 226 us against 199 us for 2,048 tokens at 28 heads, 4 key/value heads of 128)."""
+    import os
+    return 64 if os.environ.get("TESSWEAVE_SIGMOID_KEY_TILE") == "64" else 128
+
+
 def sigmoid_attention_tcgen05(dtype: torch.dtype, head_dim: int, n_kv_heads: int, page_size: int, max_q_len: int) -> bool:
     """Whether a step whose longest portion has ``max_q_len`` tokens runs its sigmoid attention on the tcgen05 kernel
-    (csrc/sigmoid_attention_tcgen05.cu): bfloat16, head size 64 or 128, pages that divide a tile of 128 keys or are a
+    (csrc/sigmoid_attention_tcgen05.cu): bfloat16, head size 64 or 128, pages that divide a tile of 64 keys or are a
     multiple of it, folded queries of 128 rows that leave room for three chunks of keys in shared memory, and a
     portion of at least 128 tokens.  TESSWEAVE_SIGMOID_PREFILL=mma|tcgen05 forces one of the two (the latter only
     for shapes the kernel takes)."""
     import os
     if dtype != torch.bfloat16 or head_dim not in (64, 128) or page_size < 4:
         return False
-    if not (128 % page_size == 0 or page_size % 128 == 0):
+    tile = sigmoid_tcgen05_key_tile()
+    if not (tile % page_size == 0 or page_size % tile == 0):
         return False
-    chunk = (head_dim // 64) * 16384
-    if (227 * 1024 - 1024 - 512 - n_kv_heads * chunk) // chunk < 3:
+    blocks = head_dim // 64
+    if (227 * 1024 - 1024 - 512 - n_kv_heads * blocks * 16384) // (blocks * tile * 128) < 3:
         return False
     forced = os.environ.get("TESSWEAVE_SIGMOID_PREFILL")
     if forced == "mma":
@@ -302,7 +311,8 @@ def sigmoid_attention_prefill_tcgen05(out, qf, bias, gate, seq_q_start, seq_q_le
     _need(out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0, "tcgen05 sigmoid attention: rows of out must be 16-byte aligned")
     _need(gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0),
           "tcgen05 sigmoid attention: rows of the gate must be 16-byte aligned")
-    code = _fn("sigmoid_attention_tcgen05", "tw_sigattn_prefill_tc5", {"TW_HEAD_DIM": head_dim})(
+    code = _fn("sigmoid_attention_tcgen05", "tw_sigattn_prefill_tc5",
+               {"TW_HEAD_DIM": head_dim, "TW_SIG_KEY_TILE": sigmoid_tcgen05_key_tile()})(
         _ptr(out), c_int(out.stride(0)), _ptr(qf), _ptr(bias), _ptr(gate), c_int(0 if gate is None else gate.stride(0)),
         _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(seq_slot), _ptr(block_table),
         c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_seqs), c_int(max_q_len), c_int(n_q_heads),

@@ -7,7 +7,7 @@
 // no maximum, no normalisation, so nothing is rescaled and partial sums over slices of keys just add.
 //
 // Keys and values reach shared memory in *chunks*: 64 keys of one key/value head, rows padded by 16 bytes
-// (conflict-free ldmatrix for every head size), through a ring of three cp.async stages.  A tile of 64 keys is
+// (conflict-free ldmatrix for every head size), through a ring of four cp.async stages.  A tile of 64 keys is
 // the chunks K_0 .. K_{G-1} (scores accumulate over them) followed by the value chunk(s).  Keys a row must not
 // see get weight 0, and their rows are zero-filled in shared memory, so nothing of a page that was freed or
 // never written reaches a sum.
@@ -32,7 +32,7 @@ constexpr int D = TW_HEAD_DIM;
 constexpr int BN = 64;                      // keys per tile
 constexpr int KSTR = D + 8;                 // padded row of a chunk (elements)
 constexpr int CHUNK = BN * KSTR;            // elements per stage
-constexpr int NSTAGE = 3;
+constexpr int NSTAGE = 4;                   // three chunks are under way while one is consumed
 constexpr int THREADS = 128;             // of the single-token kernel; the prompt kernel has 32 x its warps
 static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
 
@@ -171,17 +171,17 @@ sigattn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __res
         }
         cp_async_commit();
     };
-    issue(0);
-    issue(1);
+    for (int n = 0; n < NSTAGE - 1; ++n) issue(n);
     float S[8][4], O[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) { O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f; }
     const float b = bias ? bias[h] : 0.f;
     const int g = lane >> 2, tq = lane & 3;
     for (int n = 0; n < nchunks; ++n) {
-        issue(n + 2);
-        cp_async_wait<2>();
+        // chunk n has landed for every thread, and every warp is done with chunk n - 1, whose stage is filled next
+        cp_async_wait<NSTAGE - 2>();
         __syncthreads();
+        issue(n + NSTAGE - 1);
         const int t = n / per_tile, k = n - t * per_tile;
         const bf16* stage = ring + (n % NSTAGE) * CHUNK;
         if (k < G) {
@@ -215,7 +215,6 @@ sigattn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __res
                 values_step(O, pa, stage, kk * 16, lane);
             }
         }
-        __syncthreads();
     }
     // the output gate, then rows g and g + 8 of the warp's sixteen
 #pragma unroll
@@ -292,8 +291,7 @@ sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, 
         }
         cp_async_commit();
     };
-    issue(0);
-    issue(1);
+    for (int n = 0; n < NSTAGE - 1; ++n) issue(n);
     float S[MT][2][4], O[MT][D / 8][4], w[MT][2][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
@@ -312,9 +310,10 @@ sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, 
         c_b[m] = head_b < H ? head_b / group : -1;
     }
     for (int n = 0; n < nchunks; ++n) {
-        issue(n + 2);
-        cp_async_wait<2>();
+        // chunk n has landed for every thread, and every warp is done with chunk n - 1, whose stage is filled next
+        cp_async_wait<NSTAGE - 2>();
         __syncthreads();
+        issue(n + NSTAGE - 1);
         const int t = n / per_tile, k = n - t * per_tile;
         const bf16* stage = ring + (n % NSTAGE) * CHUNK;
         if (k < G) {
@@ -356,7 +355,6 @@ sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, 
                 values_step(O[m], pa, stage, warp * 16, lane);
             }
         }
-        __syncthreads();
     }
     // the four warps' sums meet in shared memory (the ring is free now), in warp order, one tile of heads at a time
     cp_async_wait<0>();
@@ -393,8 +391,17 @@ __global__ void sigattn_decode_merge_kernel(bf16* __restrict__ out, int out_stri
     const int row = seq_q_start[s];
     const int width = H * D;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < width; i += gridDim.x * blockDim.x) {
+        const float* src = partial + (size_t)s * nsplit * width + i;
         float acc = 0.f;
-        for (int sp = 0; sp < nsplit; ++sp) acc += partial[((size_t)s * nsplit + sp) * width + i];
+        int sp = 0;
+        for (; sp + 8 <= nsplit; sp += 8) {              // eight loads under way, added in slice order
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = src[(size_t)(sp + k) * width];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc += v[k];
+        }
+        for (; sp < nsplit; ++sp) acc += src[(size_t)sp * width];
         if (gate) acc *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)row * gate_stride + i])));
         out[(size_t)row * out_stride + i] = __float2bfloat16_rn(acc);
     }
@@ -455,7 +462,7 @@ TW_EXPORT int tw_sigattn_decode(void* out, int out_stride, float* partial, const
                          (const bf16*)v_cache, H, G, page_size, num_pages, window, nsplit, status);
     if (code != 0) return code;
     const int width = H * D;
-    const dim3 mgrid((width + 255) / 256 < 16 ? (width + 255) / 256 : 16, n_seqs);
+    const dim3 mgrid((width + 255) / 256, n_seqs);
     return tw_launch(sigattn_decode_merge_kernel, mgrid, dim3(256), 0, stream, 1, (bf16*)out, out_stride,
                      (const float*)partial, (const bf16*)gate, gate_stride, seq_q_start, seq_q_len, H, nsplit);
 }

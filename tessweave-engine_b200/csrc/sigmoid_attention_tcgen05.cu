@@ -2,7 +2,7 @@
 // size (compile with -DTW_HEAD_DIM=64 or 128).  What is computed: see the top of sigmoid_attention.cu.
 //
 // A block serves 128 rows of one (request, key/value head c), a row being a (token, query head of c's group)
-// pair, and walks the request's keys in tiles of 128.  Per key tile:
+// pair, and walks the request's keys in tiles of 128 (or 64: -DTW_SIG_KEY_TILE).  Per key tile:
 //     S = sum over key/value heads g of  Qf_g K_g^T     tcgen05.mma accumulating over the G chunks of the folded
 //                                                       query (K-major, shared memory); S (fp32) in tensor memory
 //     P = sigmoid(S + b_h), 0 where a key is not seen    four warps, one row (one TMEM lane) per thread: tcgen05.ld,
@@ -23,6 +23,9 @@
 #ifndef TW_HEAD_DIM
 #define TW_HEAD_DIM 128
 #endif
+#ifndef TW_SIG_KEY_TILE
+#define TW_SIG_KEY_TILE 128
+#endif
 
 namespace {
 
@@ -32,15 +35,17 @@ constexpr int D = TW_HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 sigmoid attention is built for head sizes 64 and 128");
 
 constexpr int BM = 128;                       // rows of a block = TMEM lanes
-constexpr int BN = 128;                       // keys per tile
-constexpr int KB = D / 64;                    // 64-column blocks of a row of k or v
-constexpr int BLK = 128 * 128;                // bytes of a [128 rows][64 columns] swizzled block
-constexpr int CHUNK_BYTES = KB * BLK;         // 128 keys of one key/value head
-constexpr int MAX_K_STAGES = 8, MAX_V_STAGES = 2;
-constexpr int BARRIER_BYTES = 512;
+constexpr int BN = TW_SIG_KEY_TILE;           // keys per tile (64 or 128): small chunks make the rings beside the folded queries deep
+static_assert(BN == 64 || BN == 128, "key tiles of 64 or 128");
+constexpr int KB = D / 64;                    // 64-column blocks of a row of q, k or v
+constexpr int BLK = BM * 128;                 // bytes of a [128 rows][64 columns] swizzled block (the queries)
+constexpr int KBLK = BN * 128;                // bytes of a [64 keys][64 columns] swizzled block (keys and values)
+constexpr int CHUNK_BYTES = KB * KBLK;        // 64 keys of one key/value head
+constexpr int MAX_K_STAGES = 12, MAX_V_STAGES = 3;
+constexpr int BARRIER_BYTES = 512;            // 2 x 12 + 2 x 3 + 6 barriers of 8 bytes, the tensor-memory slot, the abort flag
 constexpr int THREADS = 320;                  // warp 0: TMA, warp 1: MMA, warps 2-5 / 6-9: sigmoids of even / odd key tiles
-constexpr int TMEM_COLS = 512;                // two buffers of S (2 x 128 columns; P over the first 64 of each), then O (D)
-constexpr int O_COL = 256;
+constexpr int O_COL = 2 * BN;                  // two buffers of S (2 x BN columns; P over the first half of each), then O (D)
+constexpr int TMEM_COLS = O_COL + D <= 256 ? 256 : 512;
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -114,24 +119,31 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         *aborted = 0;
         mbar_fence_init();
     }
-    // One chunk (128 keys of key/value head `head` of key tile i): one TMA box per page and 64 columns of d;
-    // lane b owns box b.  `use` counts the uses of the ring so far.  False if a wait ran out.
+    // Where the boxes of key tile i lie: one TMA box per page and 64 columns of d, lane b owns box b.  The page and
+    // the place inside it are the same for every key/value head and for keys and values, so they are looked up once
+    // per tile (and one tile ahead: the producer's path from a free stage to the copy has no global load in it).
     const int box_rows = min(page_size, BN);
     const int boxes = BN / box_rows;
-    auto issue_chunk = [&](unsigned char* ring, uint64_t* full, uint64_t* empty, int stages, int use,
-                           const CUtensorMap* map, int i, int head) -> bool {
-        const int st = use % stages;
-        const uint32_t parity = (use / stages) & 1;
-        int row_coord = -1;
-        if (lane < boxes) {
+    auto look_up = [&](int i) -> int {
+        int base = -1;
+        if (lane < boxes && i < ntiles) {
             const int key0 = (j_begin + i) * BN + lane * box_rows;
             if (key0 < kv_len) {
                 const int blk = key0 / page_size;
                 const int page = blk < table_stride ? table[blk] : -1;
                 if (page < 0 || page >= num_pages) atomicOr(status, TW_ERR_PAGE);
-                else row_coord = (page * Hkv + head) * page_size + (key0 - blk * page_size);
+                else base = page * Hkv * page_size + (key0 - blk * page_size);
             }
         }
+        return base;
+    };
+    // One chunk (BN keys of key/value head `head`) of the tile whose boxes start at `base`.  `use` counts the uses of
+    // the ring so far.  False if a wait ran out.
+    auto issue_chunk = [&](unsigned char* ring, uint64_t* full, uint64_t* empty, int stages, int use,
+                           const CUtensorMap* map, int base, int head) -> bool {
+        const int st = use % stages;
+        const uint32_t parity = (use / stages) & 1;
+        const int row_coord = base >= 0 ? base + head * page_size : -1;
         const uint32_t bytes = (uint32_t)__popc(__ballot_sync(0xffffffffu, row_coord >= 0)) * KB * box_rows * 128;
         int ok = 1;
         if (lane == 0) {
@@ -143,7 +155,7 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         if (row_coord >= 0) {
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb)
-                tma_load_2d(ring + (size_t)st * CHUNK_BYTES + kb * BLK + lane * box_rows * 128, map, &full[st], kb * 64, row_coord);
+                tma_load_2d(ring + (size_t)st * CHUNK_BYTES + kb * KBLK + lane * box_rows * 128, map, &full[st], kb * 64, row_coord);
         }
         return true;
     };
@@ -151,11 +163,13 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     // the key chunks of the first tile need nothing of what follows: the producer warp asks for as many as the ring
     // holds now, and the other warps bring the query rows in meanwhile
     int k_issued = 0, v_issued = 0;
-    const int k_total = ntiles * Hkv;
+    int base_cur = -1, base_next = -1;          // boxes of tile i and of tile i + 1 (producer warp only)
     if (warp == 0) {
         __syncwarp();
+        base_cur = look_up(0);
+        base_next = look_up(1);
         while (k_issued < Hkv && k_issued < k_stages &&
-               issue_chunk(k_s, k_full, k_empty, k_stages, k_issued, &map_k, 0, k_issued)) ++k_issued;
+               issue_chunk(k_s, k_full, k_empty, k_stages, k_issued, &map_k, base_cur, k_issued)) ++k_issued;
     }
     // the block's folded query rows into shared memory, in the swizzled K-major layout (rows beyond the portion are
     // zero); eight 16-byte loads of a thread are under way before the first store
@@ -201,18 +215,21 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         // ---- producer, in the order the tensor cores use things: K of tile 0; then K of tile i + 1 and V of tile i
         bool ok = !*aborted;
         while (ok && k_issued < Hkv) {
-            ok = issue_chunk(k_s, k_full, k_empty, k_stages, k_issued, &map_k, 0, k_issued);
+            ok = issue_chunk(k_s, k_full, k_empty, k_stages, k_issued, &map_k, base_cur, k_issued);
             if (ok) ++k_issued;
         }
         for (int i = 0; ok && i < ntiles; ++i) {
+            const int base_after = look_up(i + 2);       // asked for now, used one round later
             for (int c = 0; ok && i + 1 < ntiles && c < Hkv; ++c) {
-                ok = issue_chunk(k_s, k_full, k_empty, k_stages, k_issued, &map_k, i + 1, c);
+                ok = issue_chunk(k_s, k_full, k_empty, k_stages, k_issued, &map_k, base_next, c);
                 if (ok) ++k_issued;
             }
             if (ok) {
-                ok = issue_chunk(v_s, v_full, v_empty, v_stages, v_issued, &map_v, i, kvh);
+                ok = issue_chunk(v_s, v_full, v_empty, v_stages, v_issued, &map_v, base_cur, kvh);
                 if (ok) ++v_issued;
             }
+            base_cur = base_next;
+            base_next = base_after;
         }
         if (ok && tail_rows && v_issued == ntiles) {
             // The last tile reaches past the request's last key.  What its value rows hold there must not reach a
@@ -222,7 +239,7 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 unsigned char* vt = v_s + (size_t)(last % v_stages) * CHUNK_BYTES;
                 for (int idx = lane; idx < tail_rows * KB * 8; idx += 32) {
                     const int r = BN - tail_rows + idx / (KB * 8), rest = idx % (KB * 8);
-                    *reinterpret_cast<uint4*>(vt + (rest >> 3) * BLK + r * 128 + ((rest & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(vt + (rest >> 3) * KBLK + r * 128 + ((rest & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 fence_proxy_async();
                 __syncwarp();
@@ -236,12 +253,11 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
             for (int u = max(0, k_issued - k_stages); u < k_issued; ++u) mbar_wait(&k_full[u % k_stages], (u / k_stages) & 1, status);
             for (int u = max(0, v_issued - v_stages); u < v_issued; ++u) mbar_wait(&v_full[u % v_stages], (u / v_stages) & 1, status);
         }
-        (void)k_total;
     } else if (warp == 1) {
         // ---- tensor cores: lane 0 issues every MMA of the block
         if (lane == 0 && ntiles > 0) {
             const uint32_t idesc_s = instr_desc(BN), idesc_o = instr_desc(D, true);
-            const uint64_t q_desc = smem_desc(q_s, 0), k_desc = smem_desc(k_s, 0), v_desc = smem_desc_mn_major(v_s, BLK);
+            const uint64_t q_desc = smem_desc(q_s, 0), k_desc = smem_desc(k_s, 0), v_desc = smem_desc_mn_major(v_s, KBLK);
             int k_used = 0;
             bool ok = true;
             // S of key tile i into buffer i & 1: G chunks of the folded query against the keys of G key/value heads
@@ -258,7 +274,7 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                     for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            umma_bf16(tmem_base + x * BN, qd + (uint64_t)(kb * (BLK >> 4) + k * 2), kd + (uint64_t)(kb * (BLK >> 4) + k * 2),
+                            umma_bf16(tmem_base + x * BN, qd + (uint64_t)(kb * (BLK >> 4) + k * 2), kd + (uint64_t)(kb * (KBLK >> 4) + k * 2),
                                       idesc_s, (c > 0 || kb > 0 || k > 0) ? 1u : 0u);
                     umma_commit(&k_empty[st]);
                 }
@@ -325,9 +341,9 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
                 }
                 v[c >> 1] = pack_bf16(p0, p1);
             }
-            // P over the first 64 columns of S: the whole row of S is in registers by now
-            tmem_st32_nowait(s_addr, v);
-            tmem_st32_nowait(s_addr + 32, v + 32);
+            // P over the first half of S's columns: the whole row of S is in registers by now
+#pragma unroll
+            for (int c = 0; c < BN / 2; c += 32) tmem_st32_nowait(s_addr + c, v + c);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
@@ -383,13 +399,13 @@ sigattn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-// Ring depths for G key/value heads: what is left of 227 KB beside the folded queries, in chunks of 128 keys; one or
-// two go to the values, up to eight to the keys.  False if fewer than three chunks fit.
+// Ring depths for G key/value heads: what is left of 227 KB beside the folded queries, in chunks of one key tile; one
+// to three go to the values, up to twelve to the keys.  False if fewer than three chunks fit.
 bool ring_depths(int G, int* k_stages, int* v_stages, size_t* smem) {
     const long long fixed = 1024 + BARRIER_BYTES + (long long)G * KB * BLK;
     const long long n = (227ll * 1024 - fixed) / CHUNK_BYTES;
     if (n < 3) return false;
-    *v_stages = n >= 6 ? 2 : 1;
+    *v_stages = n >= 9 ? 3 : (n >= 5 ? 2 : 1);
     *k_stages = (int)(n - *v_stages < MAX_K_STAGES ? n - *v_stages : MAX_K_STAGES);
     *smem = (size_t)(fixed + (long long)(*k_stages + *v_stages) * CHUNK_BYTES);
     return true;
