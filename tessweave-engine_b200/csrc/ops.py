@@ -225,16 +225,25 @@ def sigmoid_attention_tensor_cores(dtype: torch.dtype, head_dim: int, n_kv_heads
     return 64 * (n_kv_heads * head_dim + 8) * 2 + 4 * 64 * (head_dim + 8) * 2 <= 227 * 1024
 
 
+def sigmoid_decode_heads_per_block() -> int:
+    """0: a block of the sliced-keys kernel serves up to 32 heads of a request (the keys are read once for all of
+    them); TESSWEAVE_SIGMOID_DECODE_HEADS=16 forces blocks of 16 heads (half the registers, the keys read twice)."""
+    import os
+    return 16 if os.environ.get("TESSWEAVE_SIGMOID_DECODE_HEADS") == "16" else 0
+
+
 def sigmoid_decode_splits(n_seqs: int, n_heads: int, max_kv_len: int) -> int:
     """Slices a single token's keys are cut into: enough blocks (request x up to 32 heads x slice) for two per SM,
-    at least two tiles of 64 keys per slice, at most 64 slices."""
+    at least one tile of 64 keys per slice, at most 64 slices.  A block streams its slice slowly (it waits on its own
+    chain of dependent tensor-core products), so the bandwidth comes from the number of blocks: one request with 4,096
+    keys takes 24 us with 32 slices and 18 us with 64."""
     import os
     forced = os.environ.get("TESSWEAVE_SIGMOID_DECODE_SPLITS")
     tiles = max(1, -(-max_kv_len // 64))
     if forced:
         return max(1, min(int(forced), 64, tiles))
-    groups = max(1, n_seqs * -(-n_heads // (32 if n_heads > 16 else 16)))
-    return max(1, min((2 * _SM_COUNT) // groups, tiles // 2, 64))
+    groups = max(1, n_seqs * -(-n_heads // (32 if n_heads > 16 and not sigmoid_decode_heads_per_block() else 16)))
+    return max(1, min((2 * _SM_COUNT) // groups, tiles, 64))
 
 
 def _sigattn_checks(out, qf, bias, gate, block_table, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim):
@@ -334,8 +343,8 @@ def sigmoid_attention_decode(out, partial, qf, bias, gate, seq_q_start, seq_q_le
         _ptr(out), c_int(out.stride(0)), _ptr(partial), _ptr(qf), _ptr(bias), _ptr(gate),
         c_int(0 if gate is None else gate.stride(0)), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(seq_slot),
         _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_seqs), c_int(n_q_heads),
-        c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), c_int(window), c_int(nsplit), _ptr(status),
-        _stream())
+        c_int(n_kv_heads), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), c_int(window), c_int(nsplit),
+        c_int(sigmoid_decode_heads_per_block()), _ptr(status), _stream())
     _check(code, "sigmoid_attention_decode")
 
 

@@ -115,6 +115,48 @@ __device__ __forceinline__ void values_step(float (&O)[D / 8][4], const uint32_t
     }
 }
 
+// The same for MT tiles of sixteen rows against ONE slab of sixteen keys (the single-token kernel): a fragment of
+// the keys is loaded once and meets every row tile, and the products of different row tiles do not wait for one another.
+template <int MT>
+__device__ __forceinline__ void scores_slab(float (&S)[MT][2][4], const bf16* qs, int qstr, int c, const bf16* ks, int key0,
+                                            int lane, int live_tiles) {
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_key = key0 + (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int kd = 0; kd < D / 16; ++kd) {
+        uint32_t b[4];
+        ldmatrix_x4(b, ks + b_key * KSTR + kd * 16 + b_col);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < live_tiles) {
+                uint32_t a[4];
+                ldmatrix_x4(a, qs + (size_t)(m * 16 + a_row) * qstr + c * D + kd * 16 + a_col);
+                mma_bf16(S[m][0], a, b[0], b[1]);
+                mma_bf16(S[m][1], a, b[2], b[3]);
+            }
+        }
+    }
+}
+
+// O[m] += P[m](16 rows x 16 keys) . V(keys key0 .. key0 + 15) for the row tiles whose bit is set in `use`.
+template <int MT>
+__device__ __forceinline__ void values_slab(float (&O)[MT][D / 8][4], const uint32_t (&pa)[MT][4], const bf16* vs, int key0,
+                                            int lane, int use) {
+    const int v_key = key0 + (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
+#pragma unroll
+    for (int nd = 0; nd < D / 16; ++nd) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vs + v_key * KSTR + nd * 16 + v_col);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (use & (1 << m)) {
+                mma_bf16(O[m][2 * nd], pa[m], b[0], b[1]);
+                mma_bf16(O[m][2 * nd + 1], pa[m], b[2], b[3]);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Prompt portions.
 // ---------------------------------------------------------------------------------------
@@ -316,44 +358,47 @@ sigattn_decode_kernel(float* __restrict__ partial, const bf16* __restrict__ qf, 
         issue(n + NSTAGE - 1);
         const int t = n / per_tile, k = n - t * per_tile;
         const bf16* stage = ring + (n % NSTAGE) * CHUNK;
+        const int live_tiles = (heads + 15) >> 4;
         if (k < G) {
+            if (k == 0) {
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                if (m * 16 >= heads) continue;
-                if (k == 0) {
+                for (int m = 0; m < MT; ++m) {
 #pragma unroll
                     for (int i = 0; i < 2; ++i) { S[m][i][0] = S[m][i][1] = S[m][i][2] = S[m][i][3] = 0.f; }
                 }
-                scores_chunk<2>(S[m], qs, QSTR, m * 16, k, stage, warp * 16, lane);
             }
+            scores_slab<MT>(S, qs, QSTR, k, stage, warp * 16, lane, live_tiles);
         } else {
             const int c = c_lo + (k - G);
+            if (k == G) {
+                const int jbase = (t_first + t) * BN + warp * 16;
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                if (m * 16 >= heads) continue;
-                if (k == G) {
-                    const int jbase = (t_first + t) * BN + warp * 16;
+                for (int m = 0; m < MT; ++m) {
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int je = jbase + nt * 8 + 2 * tq + (e & 1);
-                            const bool ok = je >= j_lo && je < j_hi && ((e & 2) ? c_b[m] : c_a[m]) >= 0;
+                            const bool ok = m < live_tiles && je >= j_lo && je < j_hi && ((e & 2) ? c_b[m] : c_a[m]) >= 0;
                             w[m][nt][e] = ok ? sigmoid_fast(S[m][nt][e] + ((e & 2) ? b_b[m] : b_a[m])) : 0.f;
                         }
                     }
                 }
+            }
+            uint32_t pa[MT][4];
+            int use = 0;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
                 // does any head of this tile of sixteen take its values from key/value head c?
                 const int m_lo = (h0 + m * 16) / group, m_hi = (min(H, h0 + m * 16 + 16) - 1) / group;
-                if (c < m_lo || c > m_hi) continue;
+                if (m < live_tiles && c >= m_lo && c <= m_hi) use |= 1 << m;
                 const bool use_a = c_a[m] == c, use_b = c_b[m] == c;
-                uint32_t pa[4];
-                pa[0] = use_a ? pack_bf16(w[m][0][0], w[m][0][1]) : 0u;
-                pa[1] = use_b ? pack_bf16(w[m][0][2], w[m][0][3]) : 0u;
-                pa[2] = use_a ? pack_bf16(w[m][1][0], w[m][1][1]) : 0u;
-                pa[3] = use_b ? pack_bf16(w[m][1][2], w[m][1][3]) : 0u;
-                values_step(O[m], pa, stage, warp * 16, lane);
+                pa[m][0] = use_a ? pack_bf16(w[m][0][0], w[m][0][1]) : 0u;
+                pa[m][1] = use_b ? pack_bf16(w[m][0][2], w[m][0][3]) : 0u;
+                pa[m][2] = use_a ? pack_bf16(w[m][1][0], w[m][1][1]) : 0u;
+                pa[m][3] = use_b ? pack_bf16(w[m][1][2], w[m][1][3]) : 0u;
             }
+            values_slab<MT>(O, pa, stage, warp * 16, lane, use);
         }
     }
     // the four warps' sums meet in shared memory (the ring is free now), in warp order, one tile of heads at a time
@@ -445,11 +490,11 @@ TW_EXPORT int tw_sigattn_decode(void* out, int out_stride, float* partial, const
                                 const void* gate, int gate_stride, const int* seq_q_start, const int* seq_q_len,
                                 const int* seq_kv_len, const int* seq_slot, const int* block_table, int table_stride,
                                 const void* k_cache, const void* v_cache, int n_seqs, int H, int G, int page_size,
-                                int num_pages, int window, int nsplit, int* status, cudaStream_t stream) {
+                                int num_pages, int window, int nsplit, int heads_per_block, int* status, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (G <= 0 || H % G || nsplit <= 0) return (int)cudaErrorInvalidValue;
     // a block serves 32 heads where there are more than 16 (the keys are then read once for all of them)
-    const bool two = H > 16 && (size_t)tw_sigattn_decode_smem(G, 32) <= 227 * 1024;
+    const bool two = H > 16 && heads_per_block != 16 && (size_t)tw_sigattn_decode_smem(G, 32) <= 227 * 1024;
     const int hb = two ? 32 : 16;
     const size_t smem = (size_t)tw_sigattn_decode_smem(G, hb);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
