@@ -300,7 +300,7 @@ SCHEDULES = {
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_cutting_gives_the_plain_logits(name, dtype, folders, plain_rows, tmp_path):
     """Whole prompts; most of a prompt and its last 32 tokens one by one; portions down to two tokens; token by
     token from the first; four live requests in mixed batches with so few pages and slots that both are used
@@ -312,6 +312,30 @@ def test_every_cutting_gives_the_plain_logits(name, dtype, folders, plain_rows, 
                                  max_tokens=max_live_tokens(steps))
         assert rows, kind
         compare(rows, plain_rows[name], dtype, f"{name} {kind}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_and_short_portions_and_single_tokens_in_one_step(dtype, folders, plain_rows, tmp_path):
+    """One step carries a portion of 150 tokens (which the tcgen05 kernel takes in bfloat16), portions of 3 and 40, and
+    single tokens of two requests with keys in the cache; the next step continues all of them."""
+    name = "C"
+    vocab = LINURAX_CONFIGS[name]["vocab"]
+    reqs = {"long": random_tokens(vocab, 300, 90), "tiny": random_tokens(vocab, 9, 91), "mid": random_tokens(vocab, 90, 92),
+            "one": random_tokens(vocab, 70, 93), "two": random_tokens(vocab, 131, 94)}
+    plan = [{"one": 68, "two": 129}, {"long": 150, "tiny": 3, "mid": 40, "one": 1, "two": 1},
+            {"long": 150, "tiny": 6, "mid": 50, "one": 1, "two": 1}]
+    at = {k: 0 for k in reqs}
+    steps = []
+    for i, counts in enumerate(plan):
+        entries = []
+        for rid, n in counts.items():
+            entries.append({"id": rid, "tokens": reqs[rid][at[rid]:at[rid] + n], "want": list(range(n))})
+            at[rid] += n
+        steps.append({"step": i, "entries": entries, "end": [rid for rid in counts if at[rid] == len(reqs[rid])]})
+    assert all(at[k] == len(v) for k, v in reqs.items())
+    rows = replay_in_process(folders[name], dtype, steps, tmp_path / "out", block_size=LINURAX_PAGE[name], max_tokens=1024)
+    want = {rid: plain.logits_of(folders[name], toks).numpy() for rid, toks in reqs.items()}
+    compare(rows, want, dtype, "long and short portions beside single tokens")
 
 
 def test_batches_do_not_change_a_request(folders, tmp_path):

@@ -34,7 +34,14 @@ LINURAX_C = {
                mingru(64, ff=136)],
 }
 
-LINURAX_CONFIGS = {"A": LINURAX_A, "B": LINURAX_B, "C": LINURAX_C}
-LINURAX_PAGE = {"A": 8, "B": 4, "C": 16}
-LINURAX_SEEDS = {"A": 5, "B": 6, "C": 7}
-LINURAX_STD = {"A": 0.12, "B": 0.2, "C": 0.08}
+# sizes no fast path takes: a width that is no multiple of 8, a head size that is no multiple of 8, five heads that
+# are their own key/value heads, odd recurrent and feed-forward sizes, an odd vocabulary
+LINURAX_D = {
+    "architecture": "Linurax", "vocab": 53, "width": 36, "embedding": {"scale": 2.5}, "norm": {"eps": 1e-4},
+    "layers": [mingru(30), attention(5, 5, 20, 10, 123.0, 0.2, ff=50), mingru(31, ff=27), attention(2, 1, 12, 12, 9.0, 0.4)],
+}
+
+LINURAX_CONFIGS = {"A": LINURAX_A, "B": LINURAX_B, "C": LINURAX_C, "D": LINURAX_D}
+LINURAX_PAGE = {"A": 8, "B": 4, "C": 16, "D": 2}
+LINURAX_SEEDS = {"A": 5, "B": 6, "C": 7, "D": 8}
+LINURAX_STD = {"A": 0.12, "B": 0.2, "C": 0.08, "D": 0.25}
