@@ -4,6 +4,7 @@ decode through the Python entry point, prefill of 2,048 tokens, and decode at ba
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C]
     python bench.py --impl reference ...      # the unmodified reference, if it is installed
     python bench.py --kernels                 # every operation of a layer alone, with its roofline
+    python bench.py --design linurax          # the Linurax decoder beside Qwen2 at equal layer sizes (a record of its own)
 
 The default run has the layer sizes of the Qwen2.5-7B-sized benchmark configuration with
 random weights (N(0, 0.02), drawn on the device), a batch of 8 and a context of 4,096 tokens.
