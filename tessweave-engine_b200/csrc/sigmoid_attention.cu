@@ -294,11 +294,17 @@ sigattn_prepare_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj, int proj_s
     const int h_per = (Hq + parts - 1) / parts;
     const int h_lo = part * h_per, h_hi = min(Hq, h_lo + h_per);
     __nv_bfloat16* out = qf + (size_t)n * Hq * KW;
-    for (int rem4 = threadIdx.x; rem4 < (KW >> 2); rem4 += blockDim.x) {
+    // a thread owns four neighbouring columns of the folded rows; where a row has fewer groups of four than the block
+    // has threads, the block's heads are shared out over the threads that own the same columns, eight at a time
+    const int col_groups = KW >> 2;
+    const int sharers = col_groups < (int)blockDim.x ? (int)blockDim.x / col_groups : 1;
+    const int share = sharers > 1 ? (int)threadIdx.x / col_groups : 0;
+    for (int rem4 = sharers > 1 ? (int)threadIdx.x % col_groups : (int)threadIdx.x;
+         rem4 < col_groups && share < sharers; rem4 += blockDim.x) {
         const int rem = rem4 << 2;
         const int c = rem / D, d = rem - c * D;
         const float* q = sq + (c * group) * D + d;
-        for (int hb = h_lo; hb < h_hi; hb += 8) {
+        for (int hb = h_lo + 8 * share; hb < h_hi; hb += 8 * sharers) {
             float4 acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
