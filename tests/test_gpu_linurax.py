@@ -180,14 +180,17 @@ def test_sigmoid_attention_alone(dtype, shape):
 
 
 @pytest.mark.parametrize("prefill", ["mma", "tcgen05"])
-@pytest.mark.parametrize("heads,kv,d,window", [(8, 2, 64, None), (20, 4, 32, None), (3, 1, 96, None), (4, 4, 128, 150), (2, 1, 16, 65),
-                                               (28, 4, 128, None), (6, 3, 64, 300)])
-def test_tensor_core_attention_against_the_exact_kernel(heads, kv, d, window, prefill, monkeypatch):
+@pytest.mark.parametrize("heads,kv,d,window,page", [
+    (8, 2, 64, None, 16), (20, 4, 32, None, 16), (3, 1, 96, None, 16), (4, 4, 128, 150, 16), (2, 1, 16, 65, 16), (28, 4, 128, None, 16),
+    (6, 3, 64, 300, 16), (40, 8, 16, None, 8),          # more heads than one block of the single-token kernel serves
+    (8, 2, 64, None, 128), (4, 2, 128, 200, 256),       # pages as long as a key tile, and longer
+    (6, 3, 64, None, 4)])                               # 32 pages to a key tile
+def test_tensor_core_attention_against_the_exact_kernel(heads, kv, d, window, page, prefill, monkeypatch):
     """bfloat16, several hundred keys: portions whose tiles end inside pages and inside tiles of 64 keys, and
     single tokens whose keys are cut into slices, through the tensor-core kernels and through the exact kernel
     (same rounded inputs, so they differ by the rounding of the weights to bfloat16 and no more).  Portions run
     on the mma.sync kernel and on the tcgen05 kernel."""
-    hidden, page = 64, 16
+    hidden = 64
     if prefill == "tcgen05" and d not in (64, 128):
         pytest.skip("the tcgen05 kernel is built for head sizes 64 and 128")
     monkeypatch.setenv("TESSWEAVE_SIGMOID_PREFILL", prefill)     # tcgen05: every portion, also the short ones
@@ -205,7 +208,7 @@ def test_tensor_core_attention_against_the_exact_kernel(heads, kv, d, window, pr
         mixer = build_part("mixer", spec, rt)
         fill(mixer, 21, 0.3)
         mixer.bias.fill_(-2.0)
-        cache = tw.CacheManager([(mixer.cache_need(), None)], page, 48, 1, 768, torch.bfloat16, rt.device, prefix_cache=False)
+        cache = tw.CacheManager([(mixer.cache_need(), None)], page, -(-768 // page), 1, 768, torch.bfloat16, rt.device, prefix_cache=False)
         lease = cache.admit(None)
         outs, p = [], 0
         for n in cuts:
