@@ -29,7 +29,11 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..parts.base import FixedState, PagedKV, PagedView, StateView
+from ..parts.base import FixedState, PagedKV, PagedView, SeveralNeeds, SeveralViews, StateView
+
+
+def _member_key(key, j: int) -> tuple:
+    return (key, j) if isinstance(key, int) else key + (j,)
 
 
 class CapacityError(RuntimeError):
@@ -60,9 +64,9 @@ class PageGroup:
         self.need, self.entries = need, entries
         self.num_pages, self.page_size = num_pages, page_size
         self.window = need.window
-        shape = (len(entries), num_pages, need.kv_heads, page_size, need.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        shape = (len(entries), num_pages, need.kv_heads, page_size)
+        self.k = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
+        self.v = torch.zeros(shape + (need.value_dim,), dtype=dtype, device=device)     # value rows may differ in length
         self.refs = [0] * num_pages
         self.free = list(reversed(range(num_pages)))    # pop() hands out low ids first
         self.promised = 0
@@ -74,7 +78,7 @@ class PageGroup:
 
     @property
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
     def unpromised_free(self) -> int:
         return len(self.free) - self.promised
@@ -92,18 +96,26 @@ class CacheManager:
         self.max_blocks = math.ceil(max_context / page_size)
         self.poison_freed = poison_freed
         self.needs = needs
-        # ---- sort the schedule entries into groups
+        # ---- sort the schedule entries into groups.  An entry's need may be several needs (a mixer made of
+        # several mixers): a plain need is keyed by its entry, a member by (entry, place inside the entry's need, ...)
         self.groups: list[PageGroup] = []
-        self.group_of_entry: dict[int, int] = {}
-        self.state: dict[int, torch.Tensor] = {}
-        by_need: dict[PagedKV, list[int]] = {}
-        for i, (need, cache_of) in enumerate(needs):
-            if isinstance(need, PagedKV):
-                by_need.setdefault(need, []).append(i)
+        self.group_of_entry: dict = {}
+        self.state: dict = {}
+        by_need: dict[PagedKV, list] = {}
+
+        def sort_in(key, need) -> None:
+            if isinstance(need, SeveralNeeds):
+                for j, member in enumerate(need.needs):
+                    sort_in(_member_key(key, j), member)
+            elif isinstance(need, PagedKV):
+                by_need.setdefault(need, []).append(key)
             elif isinstance(need, FixedState):
-                self.state[i] = torch.zeros((max_requests, need.numel), dtype=need.dtype, device=self.device)
+                self.state[key] = torch.zeros((max_requests, need.numel), dtype=need.dtype, device=self.device)
             elif need is not None:
-                raise TypeError(f"schedule entry {i}: unknown cache need {need!r}")
+                raise TypeError(f"schedule entry {key}: unknown cache need {need!r}")
+
+        for i, (need, cache_of) in enumerate(needs):
+            sort_in(i, need)
         for need, entries in by_need.items():
             gi = len(self.groups)
             self.groups.append(PageGroup(need, entries, num_pages, page_size, max_requests, self.max_blocks,
@@ -124,13 +136,18 @@ class CacheManager:
     def view(self, entry: int):
         """The cache a mixer sees for schedule entry ``entry`` (its owner's, if it reads another's)."""
         owner = self.owner_of_entry[entry]
-        if owner in self.state:
-            return StateView(self.state[owner])
-        gi = self.group_of_entry.get(owner)
+        return self._view(owner, self.needs[owner][0])
+
+    def _view(self, key, need):
+        if isinstance(need, SeveralNeeds):
+            return SeveralViews(tuple(self._view(_member_key(key, j), member) for j, member in enumerate(need.needs)))
+        if key in self.state:
+            return StateView(self.state[key])
+        gi = self.group_of_entry.get(key)
         if gi is None:
             return None
         g = self.groups[gi]
-        li = g.layer_of_entry[owner]
+        li = g.layer_of_entry[key]
         return PagedView(g.k[li], g.v[li], g.device_table, self.page_size, g.window,
                          host_tables=lambda slot, _g=gi: list(self.leases[slot].tables[_g]))
 

@@ -901,3 +901,98 @@ TW_EXPORT int tw_silu_mul(void* out, const void* gate_up, int n_rows, int inter,
                                                                         interleaved);
     return TW_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------
+// rows[n, c] += bias[c] over the first `cols` columns of each packed row, in place (fp32 sum, rounded once).
+// For mixers whose bias is not added by the kernel that follows the projection.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_bias_rows_kernel(T* __restrict__ rows, int stride, const float* __restrict__ bias, int cols) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    T* row = rows + (size_t)blockIdx.x * stride;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) row[c] = tw_from_float<T>(tw_to_float(row[c]) + bias[c]);
+}
+
+TW_EXPORT int tw_add_bias_rows(void* rows, int stride, const float* bias, int n_rows, int cols, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0 || cols <= 0) return 0;
+    if (dtype == TW_F32)
+        return tw_launch(add_bias_rows_kernel<float>, dim3(n_rows), dim3(256), 0, stream, 1, (float*)rows, stride, bias, cols);
+    return tw_launch(add_bias_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, 1, (__nv_bfloat16*)rows, stride,
+                     bias, cols);
+}
+
+// ---------------------------------------------------------------------------
+// Keys and values of the step's rows into their pages, as they stand in the packed rows (already biased and
+// rotated): k [Hkv, Dk] at column k_col, v [Hkv, Dv] at column v_col; key rows and value rows of a page may
+// differ in length.  Padding rows are skipped; a missing page sets the status bit.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ rows, int stride, int k_col, int v_col,
+                                const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                const int* __restrict__ seq_slot, const int* __restrict__ block_table, int table_stride,
+                                T* __restrict__ k_cache, T* __restrict__ v_cache, int Hkv, int Dk, int Dv, int page_size,
+                                int num_pages, int* status) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int n = blockIdx.x;
+    const int s = seq_of_token[n];
+    if (s < 0) return;
+    const int pos = positions[n];
+    const int blk = pos / page_size, in_page = pos - blk * page_size;
+    const int page = blk < table_stride ? block_table[(size_t)seq_slot[s] * table_stride + blk] : -1;
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(status, TW_ERR_PAGE);
+        return;
+    }
+    const T* row = rows + (size_t)n * stride;
+    for (int i = threadIdx.x; i < Hkv * Dk; i += blockDim.x) {
+        const int h = i / Dk, d = i - h * Dk;
+        k_cache[(((size_t)page * Hkv + h) * page_size + in_page) * Dk + d] = row[k_col + i];
+    }
+    for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
+        const int h = i / Dv, d = i - h * Dv;
+        v_cache[(((size_t)page * Hkv + h) * page_size + in_page) * Dv + d] = row[v_col + i];
+    }
+}
+
+TW_EXPORT int tw_kv_store(const void* rows, int stride, int k_col, int v_col, const int* positions, const int* seq_of_token,
+                          const int* seq_slot, const int* block_table, int table_stride, void* k_cache, void* v_cache,
+                          int n_tokens, int Hkv, int Dk, int Dv, int page_size, int num_pages, int dtype, int* status,
+                          cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (dtype == TW_F32)
+        return tw_launch(kv_store_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, 1, (const float*)rows, stride, k_col,
+                         v_col, positions, seq_of_token, seq_slot, block_table, table_stride, (float*)k_cache, (float*)v_cache,
+                         Hkv, Dk, Dv, page_size, num_pages, status);
+    return tw_launch(kv_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, 1, (const __nv_bfloat16*)rows, stride,
+                     k_col, v_col, positions, seq_of_token, seq_slot, block_table, table_stride, (__nv_bfloat16*)k_cache,
+                     (__nv_bfloat16*)v_cache, Hkv, Dk, Dv, page_size, num_pages, status);
+}
+
+// ---------------------------------------------------------------------------
+// acc = (first ? 0 : acc) + scale * x, element by element in fp32; `out` (may be null) receives the new acc in
+// the activation type.  For mixers whose result is a weighted sum of several mixers' results.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void scaled_accumulate_kernel(float* __restrict__ acc, T* __restrict__ out, const T* __restrict__ x, float scale,
+                                         int first, size_t count) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const float v = (first ? 0.f : acc[i]) + scale * tw_to_float(x[i]);
+    acc[i] = v;
+    if (out) out[i] = tw_from_float<T>(v);
+}
+
+TW_EXPORT int tw_scaled_accumulate(float* acc, void* out, const void* x, float scale, int first, long long count, int dtype,
+                                   cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const dim3 grid((unsigned)((count + 255) / 256));
+    if (dtype == TW_F32)
+        return tw_launch(scaled_accumulate_kernel<float>, grid, dim3(256), 0, stream, 1, acc, (float*)out, (const float*)x, scale,
+                         first, (size_t)count);
+    return tw_launch(scaled_accumulate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, acc, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)x, scale, first, (size_t)count);
+}

@@ -1,0 +1,224 @@
+// Linear attention as a recurrence over a matrix state of fixed size per request and head.
+//
+// A head keeps S [Dk, Dv] in fp32.  Three update rules share one kernel (rows q/r, k [Dk], v [Dv] per token):
+//
+//   TW_REC_RETENTION   S <- g S + k v^T                     o = S^T q          g a constant per head
+//                      q and k are rotated by position on the way in, k is scaled after the rotation
+//   TW_REC_WKV         o = (S + diag(u) k v^T)^T r          S <- diag(w) S + k v^T
+//                      w = exp(-exp(d + w0)) per key channel from the projected d; u a bonus for the token itself
+//   TW_REC_MLSTM       m' = max(f + m, i)                   S <- e^(f + m - m') S + e^(i - m') k v^T
+//                      n likewise with k alone;  o = S^T q,  den = max(|n . q|, e^(-m')) + 1e-6
+//                      i = cap tanh((pi + bi) / cap), f = logsigmoid(cap tanh((pf + bf) / cap)); m is 0 before
+//                      the first token.  n is carried as one more column of S (a value that is always 1).
+//
+// One block per (head, request): thread j owns column j of S in registers (TW_DK values, a compile-time
+// size) and walks the request's rows of this step in order; the rows of 16 tokens at a time are staged in
+// shared memory as fp32 (rotation, scaling, decays and gates are evaluated there, once per value).  The
+// state slot is read at the first row and written back after the last, so a request may be cut into
+// steps anywhere, and the sums at a position are formed in the same order however it was cut.  Outputs are
+// fp32; the norm over a head, the gate and the rounding follow in tw_head_norm_gate (recurrent.cu).
+#include "common.cuh"
+
+#ifndef TW_DK
+#define TW_DK 64
+#endif
+#define TW_REC_CHUNK 16
+
+enum : int { TW_REC_RETENTION = 0, TW_REC_WKV = 1, TW_REC_MLSTM = 2 };
+
+struct RecArgs {
+    float* out;                 // [rows, H * Dv] fp32
+    float* den;                 // [rows, H] fp32 (mlstm)
+    const void* q; int q_stride;        // rows of q (r), k, v: element type T, column h * D + i inside each
+    const void* k; int k_stride;
+    const void* v; int v_stride;
+    const float* wpre; int wpre_stride; // wkv: d [rows, H * Dk] fp32;  mlstm: [rows, 2 H] fp32 (pi | pf)
+    const float* p0;            // wkv: w0 [H * Dk];  retention: decay [H];  mlstm: bias [2 H]
+    const float* p1;            // wkv: u [H * Dk]
+    const float* inv_freq; int rot_dims;    // retention: rotation of the first rot_dims values of q and k
+    float k_scale, q_scale, cap;
+    float* state; long long state_stride;  // [slots, state_stride]; a head's part starts at h * head_state
+    const void* tail_src; int tail_stride, tail_width; long long tail_offset;   // wkv: row copied behind the heads
+    const int* positions;
+    const int* seq_slot; const int* seq_q_start; const int* seq_q_len;
+    int H, Dv, write_state;
+};
+
+__device__ __forceinline__ float tw_logsigmoid(float x) {
+    return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(288)
+linear_recurrence_kernel(RecArgs a) {
+    extern __shared__ float sm[];
+    constexpr int DK = TW_DK, C = TW_REC_CHUNK;
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int h = blockIdx.x, s = blockIdx.y;
+    const int len = a.seq_q_len[s];
+    if (len <= 0) return;
+    const int start = a.seq_q_start[s];
+    const int Dv = a.Dv, cols = MODE == TW_REC_MLSTM ? Dv + 1 : Dv;
+    const int j = threadIdx.x;
+    const bool live = j < cols;
+    float* sq = sm;                         // [C][DK]
+    float* sk = sq + C * DK;                // [C][DK]
+    float* sw = sk + C * DK;                // [C][DK] (wkv) or [C][2] gates (mlstm)
+    float* sv = sw + (MODE == TW_REC_WKV ? C * DK : (MODE == TW_REC_MLSTM ? 2 * C : 0));   // [C][Dv]
+    float* su = sv + C * Dv;                // [DK] bonus (wkv)
+    const long long head_state = (long long)DK * cols + (MODE == TW_REC_MLSTM ? 1 : 0);
+    float* slot = a.state + (size_t)a.seq_slot[s] * a.state_stride + (size_t)h * head_state;
+
+    float S[DK];
+    float m = 0.f;
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DK; ++i) S[i] = slot[(size_t)i * cols + j];
+    }
+    if (MODE == TW_REC_MLSTM) m = slot[(size_t)DK * cols];
+    if (MODE == TW_REC_WKV) {
+        for (int i = threadIdx.x; i < DK; i += blockDim.x) su[i] = a.p1[h * DK + i];
+    }
+    const float decay = MODE == TW_REC_RETENTION ? a.p0[h] : 0.f;
+    const int half = a.rot_dims >> 1;
+
+    for (int t0 = 0; t0 < len; t0 += C) {
+        const int ct = min(C, len - t0);
+        __syncthreads();
+        // ---- stage the rows of ct tokens as fp32
+        for (int e = threadIdx.x; e < ct * DK; e += blockDim.x) {
+            const int t = e / DK, i = e - t * DK;
+            const size_t row = (size_t)(start + t0 + t);
+            const T* qr = (const T*)a.q + row * a.q_stride + h * DK;
+            const T* kr = (const T*)a.k + row * a.k_stride + h * DK;
+            float qv = tw_to_float(qr[i]), kv = tw_to_float(kr[i]);
+            if (MODE == TW_REC_RETENTION && i < a.rot_dims) {
+                const int p = i < half ? i : i - half;
+                float sn, cs;
+                sincosf((float)a.positions[row] * a.inv_freq[p], &sn, &cs);
+                if (i < half) {
+                    qv = qv * cs - tw_to_float(qr[i + half]) * sn;
+                    kv = kv * cs - tw_to_float(kr[i + half]) * sn;
+                } else {
+                    qv = qv * cs + tw_to_float(qr[i - half]) * sn;
+                    kv = kv * cs + tw_to_float(kr[i - half]) * sn;
+                }
+            }
+            sq[e] = qv * a.q_scale;
+            sk[e] = kv * a.k_scale;
+            if (MODE == TW_REC_WKV)
+                sw[e] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
+        }
+        for (int e = threadIdx.x; e < ct * Dv; e += blockDim.x) {
+            const int t = e / Dv, c = e - t * Dv;
+            sv[e] = tw_to_float(((const T*)a.v)[(size_t)(start + t0 + t) * a.v_stride + h * Dv + c]);
+        }
+        if (MODE == TW_REC_MLSTM) {
+            for (int t = threadIdx.x; t < ct; t += blockDim.x) {
+                const float* g = a.wpre + (size_t)(start + t0 + t) * a.wpre_stride;
+                const float pi = g[h] + a.p0[h], pf = g[a.H + h] + a.p0[a.H + h];
+                sw[2 * t] = a.cap * tanhf(pi / a.cap);
+                sw[2 * t + 1] = tw_logsigmoid(a.cap * tanhf(pf / a.cap));
+            }
+        }
+        __syncthreads();
+        if (!live) continue;
+        // ---- the recurrence, token by token
+        for (int t = 0; t < ct; ++t) {
+            const float* q = sq + t * DK;
+            const float* k = sk + t * DK;
+            const float vj = (MODE == TW_REC_MLSTM && j == Dv) ? 1.f : sv[t * Dv + j];
+            float acc = 0.f;
+            if (MODE == TW_REC_RETENTION) {
+#pragma unroll
+                for (int i = 0; i < DK; ++i) {
+                    S[i] = decay * S[i] + k[i] * vj;
+                    acc += q[i] * S[i];
+                }
+            } else if (MODE == TW_REC_WKV) {
+                const float* w = sw + t * DK;
+#pragma unroll
+                for (int i = 0; i < DK; ++i) {
+                    const float kv = k[i] * vj;
+                    acc += q[i] * (S[i] + su[i] * kv);
+                    S[i] = w[i] * S[i] + kv;
+                }
+            } else {
+                const float li = sw[2 * t], lf = sw[2 * t + 1];
+                const float m_new = fmaxf(lf + m, li);
+                const float fa = expf(lf + m - m_new), fb = expf(li - m_new) * vj;
+                m = m_new;
+#pragma unroll
+                for (int i = 0; i < DK; ++i) {
+                    S[i] = fa * S[i] + fb * k[i];
+                    acc += q[i] * S[i];
+                }
+            }
+            const size_t row = (size_t)(start + t0 + t);
+            if (MODE == TW_REC_MLSTM && j == Dv)
+                a.den[row * a.H + h] = fmaxf(fabsf(acc), expf(-m)) + 1e-6f;
+            else
+                a.out[row * ((size_t)a.H * Dv) + (size_t)h * Dv + j] = acc;
+        }
+    }
+    if (!a.write_state) return;
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DK; ++i) slot[(size_t)i * cols + j] = S[i];
+    }
+    if (MODE == TW_REC_MLSTM && threadIdx.x == 0) slot[(size_t)DK * cols] = m;
+    if (MODE == TW_REC_WKV && h == 0 && a.tail_src) {
+        // what the next step's first token mixes with: the last row this mixer read
+        const T* src = (const T*)a.tail_src + (size_t)(start + len - 1) * a.tail_stride;
+        float* dst = a.state + (size_t)a.seq_slot[s] * a.state_stride + a.tail_offset;
+        for (int c = threadIdx.x; c < a.tail_width; c += blockDim.x) dst[c] = tw_to_float(src[c]);
+    }
+}
+
+template <typename T, int MODE>
+static int launch_recurrence(const RecArgs& a, int n_seqs, cudaStream_t stream) {
+    const int cols = MODE == TW_REC_MLSTM ? a.Dv + 1 : a.Dv;
+    const int threads = ((cols + 31) / 32) * 32;
+    size_t floats = 2 * TW_REC_CHUNK * TW_DK + (size_t)TW_REC_CHUNK * a.Dv + TW_DK;
+    floats += MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_DK : 2 * TW_REC_CHUNK;
+    const size_t smem = floats * sizeof(float);
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(linear_recurrence_kernel<T, MODE>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return tw_launch(linear_recurrence_kernel<T, MODE>, dim3(a.H, n_seqs), dim3(threads), smem, stream, 1, a);
+}
+
+TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void* q, int q_stride, const void* k, int k_stride,
+                                   const void* v, int v_stride, const float* wpre, int wpre_stride, const float* p0,
+                                   const float* p1, const float* inv_freq, int rot_dims, float q_scale, float k_scale,
+                                   float cap, float* state, long long state_stride, const void* tail_src, int tail_stride,
+                                   int tail_width, long long tail_offset, const int* positions, const int* seq_slot,
+                                   const int* seq_q_start, const int* seq_q_len, int n_seqs, int H, int Dk, int Dv,
+                                   int write_state, int dtype, cudaStream_t stream) {
+    if (n_seqs <= 0 || H <= 0) return 0;
+    if (Dk != TW_DK || Dv <= 0 || Dv > 256 || rot_dims < 0 || rot_dims > Dk || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
+    RecArgs a;
+    a.out = out; a.den = den; a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
+    a.wpre = wpre; a.wpre_stride = wpre_stride; a.p0 = p0; a.p1 = p1; a.inv_freq = inv_freq; a.rot_dims = inv_freq ? rot_dims : 0;
+    a.k_scale = k_scale; a.q_scale = q_scale; a.cap = cap; a.state = state; a.state_stride = state_stride;
+    a.tail_src = tail_src; a.tail_stride = tail_stride; a.tail_width = tail_width; a.tail_offset = tail_offset;
+    a.positions = positions; a.seq_slot = seq_slot; a.seq_q_start = seq_q_start; a.seq_q_len = seq_q_len;
+    a.H = H; a.Dv = Dv; a.write_state = write_state;
+    const bool f32 = dtype == TW_F32;
+    switch (mode) {
+    case TW_REC_RETENTION:
+        return f32 ? launch_recurrence<float, TW_REC_RETENTION>(a, n_seqs, stream)
+                   : launch_recurrence<__nv_bfloat16, TW_REC_RETENTION>(a, n_seqs, stream);
+    case TW_REC_WKV:
+        if (Dv != Dk) return (int)cudaErrorInvalidValue;
+        return f32 ? launch_recurrence<float, TW_REC_WKV>(a, n_seqs, stream)
+                   : launch_recurrence<__nv_bfloat16, TW_REC_WKV>(a, n_seqs, stream);
+    case TW_REC_MLSTM:
+        return f32 ? launch_recurrence<float, TW_REC_MLSTM>(a, n_seqs, stream)
+                   : launch_recurrence<__nv_bfloat16, TW_REC_MLSTM>(a, n_seqs, stream);
+    }
+    return (int)cudaErrorInvalidValue;
+}

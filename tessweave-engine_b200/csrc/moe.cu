@@ -1,0 +1,193 @@
+// Routed feed-forward (mixture of experts), weight-streaming form: every (token, chosen expert) pair is a
+// matrix-vector product of its own.  Steps with few tokens are bound by the bytes of the chosen experts'
+// matrices, which these kernels stream once per pair in 16-byte loads.
+//
+//   tw_moe_route     z = Wr h + br (fp32); the `top` largest z (lowest index first at a tie); their weights are the
+//                    softmax over those alone; optionally one more dot product per token, sigmoid(ws . h), the
+//                    gate of an expert that every token uses
+//   tw_moe_gate_up   act[token, j] = silu(Wg_e h) * (Wu_e h)          e = the j-th expert of the token
+//   tw_moe_down      out[token] = sum_j weight_j Wd_e act[token, j]  (+ gate * shared[token])
+//
+// Expert matrices are stacked: gate/up [E, 2, F, width] (a gate matrix followed by its up matrix), down
+// [E, width, F].  Dot products accumulate in fp32; the weighted sum over experts is fp32.
+#include "common.cuh"
+
+template <typename T>
+__device__ __forceinline__ float tw_dot_row(const T* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float acc = 0.f;
+    for (int i = lane; i < n; i += 32) acc += tw_to_float(w[i]) * x[i];
+    return tw_warp_sum(acc);
+}
+
+// bf16 rows whose length is a multiple of 8 and whose start is 16-byte aligned: eight values per load
+__device__ __forceinline__ float tw_dot_row8(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float acc = 0.f;
+    for (int i = lane * 8; i < n; i += 256) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(p[e]);
+            acc += f.x * x[i + 2 * e] + f.y * x[i + 2 * e + 1];
+        }
+    }
+    return tw_warp_sum(acc);
+}
+
+template <typename T> __device__ __forceinline__ float tw_dot(const T* w, const float* x, int n, int lane, bool vec);
+template <> __device__ __forceinline__ float tw_dot<float>(const float* w, const float* x, int n, int lane, bool) {
+    return tw_dot_row(w, x, n, lane);
+}
+template <> __device__ __forceinline__ float tw_dot<__nv_bfloat16>(const __nv_bfloat16* w, const float* x, int n, int lane, bool vec) {
+    return vec ? tw_dot_row8(w, x, n, lane) : tw_dot_row(w, x, n, lane);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, float* __restrict__ shared_gate,
+                 const T* __restrict__ h, int h_stride, const T* __restrict__ wr, const float* __restrict__ br,
+                 const T* __restrict__ ws, int width, int E, int top) {
+    extern __shared__ float sm[];           // [width] the row, [E + 1] logits, [E] marks
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* x = sm;
+    float* z = sm + width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) x[c] = tw_to_float(h[(size_t)row * h_stride + c]);
+    __syncthreads();
+    const bool vec = (width & 7) == 0;
+    for (int e = warp; e < E + (ws ? 1 : 0); e += 4) {
+        const float d = tw_dot<T>(e < E ? wr + (size_t)e * width : ws, x, width, lane, vec);
+        if (lane == 0) z[e] = e < E ? d + (br ? br[e] : 0.f) : d;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    if (ws && shared_gate) shared_gate[row] = 1.0f / (1.0f + expf(-z[E]));
+    // selection: `top` times the largest logit that is left; a row of NaN still names `top` different experts
+    float* taken = z + E + 1;
+    for (int e = 0; e < E; ++e) taken[e] = 0.f;
+    float best0 = 0.f, sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+        int arg = -1;
+        float best = -INFINITY;
+        for (int e = 0; e < E; ++e) {
+            if (taken[e] != 0.f) continue;
+            if (arg < 0 || z[e] > best) { arg = e; best = z[e]; }
+        }
+        taken[arg] = 1.f;
+        chosen[(size_t)row * top + j] = arg;
+        if (j == 0) best0 = best;
+        const float w = expf(best - best0);
+        weight[(size_t)row * top + j] = w;
+        sum += w;
+    }
+    for (int j = 0; j < top; ++j) weight[(size_t)row * top + j] /= sum;
+}
+
+TW_EXPORT int tw_moe_route(int* chosen, float* weight, float* shared_gate, const void* h, int h_stride, const void* wr,
+                           const float* br, const void* ws, int rows, int width, int E, int top, int dtype,
+                           cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E) return (int)cudaErrorInvalidValue;
+    const size_t smem = ((size_t)width + 2 * E + 1) * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (dtype == TW_F32)
+        return tw_launch(moe_route_kernel<float>, dim3(rows), dim3(128), smem, stream, 1, chosen, weight, shared_gate,
+                         (const float*)h, h_stride, (const float*)wr, br, (const float*)ws, width, E, top);
+    return tw_launch(moe_route_kernel<__nv_bfloat16>, dim3(rows), dim3(128), smem, stream, 1, chosen, weight, shared_gate,
+                     (const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)wr, br, (const __nv_bfloat16*)ws, width, E, top);
+}
+
+#define TW_MOE_WARPS 8
+
+template <typename T>
+__global__ void __launch_bounds__(32 * TW_MOE_WARPS)
+moe_gate_up_kernel(T* __restrict__ act, const T* __restrict__ h, int h_stride, const T* __restrict__ wgu,
+                   const int* __restrict__ chosen, int width, int F, int E, int top, int rows_per_block) {
+    extern __shared__ float sm[];           // [width]
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int pair = blockIdx.x, row = pair / top;
+    const int e = chosen[pair];
+    if (e < 0 || e >= E) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) sm[c] = tw_to_float(h[(size_t)row * h_stride + c]);
+    __syncthreads();
+    const bool vec = (width & 7) == 0;
+    const T* wg = wgu + (size_t)e * 2 * F * width;
+    const T* wu = wg + (size_t)F * width;
+    const int f0 = blockIdx.y * rows_per_block, f1 = min(F, f0 + rows_per_block);
+    for (int f = f0 + warp; f < f1; f += TW_MOE_WARPS) {
+        const float g = tw_dot<T>(wg + (size_t)f * width, sm, width, lane, vec);
+        const float u = tw_dot<T>(wu + (size_t)f * width, sm, width, lane, vec);
+        if (lane == 0) act[(size_t)pair * F + f] = tw_from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+TW_EXPORT int tw_moe_gate_up(void* act, const void* h, int h_stride, const void* wgu, const int* chosen, int rows, int width,
+                             int F, int E, int top, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    // enough blocks to fill the GPU when there are few pairs, whole rounds of warps per block
+    int per = F;
+    while (per > 4 * TW_MOE_WARPS && (size_t)rows * top * ((F + per - 1) / per) < 592) per = (per + 1) / 2;
+    per = ((per + TW_MOE_WARPS - 1) / TW_MOE_WARPS) * TW_MOE_WARPS;
+    const dim3 grid(rows * top, (F + per - 1) / per);
+    if (dtype == TW_F32)
+        return tw_launch(moe_gate_up_kernel<float>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (float*)act, (const float*)h,
+                         h_stride, (const float*)wgu, chosen, width, F, E, top, per);
+    return tw_launch(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (__nv_bfloat16*)act,
+                     (const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)wgu, chosen, width, F, E, top, per);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(32 * TW_MOE_WARPS)
+moe_down_kernel(T* __restrict__ out, const T* __restrict__ act, const T* __restrict__ wd, const int* __restrict__ chosen,
+                const float* __restrict__ weight, const T* __restrict__ shared, const float* __restrict__ shared_gate,
+                int width, int F, int E, int top, int cols_per_block) {
+    extern __shared__ float sm[];           // [top][F] the activations of the token's experts
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < top * F; i += blockDim.x) sm[i] = tw_to_float(act[(size_t)row * top * F + i]);
+    __syncthreads();
+    const bool vec = (F & 7) == 0;
+    const float sg = shared ? (shared_gate ? shared_gate[row] : 1.f) : 0.f;
+    const int c0 = blockIdx.y * cols_per_block, c1 = min(width, c0 + cols_per_block);
+    for (int c = c0 + warp; c < c1; c += TW_MOE_WARPS) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int e = chosen[(size_t)row * top + j];
+            if (e < 0 || e >= E) continue;
+            acc += weight[(size_t)row * top + j] * tw_dot<T>(wd + ((size_t)e * width + c) * F, sm + (size_t)j * F, F, lane, vec);
+        }
+        if (lane == 0) {
+            if (shared) acc += sg * tw_to_float(shared[(size_t)row * width + c]);
+            out[(size_t)row * width + c] = tw_from_float<T>(acc);
+        }
+    }
+}
+
+TW_EXPORT int tw_moe_down(void* out, const void* act, const void* wd, const int* chosen, const float* weight,
+                          const void* shared, const float* shared_gate, int rows, int width, int F, int E, int top, int dtype,
+                          cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t smem = (size_t)top * F * sizeof(float);
+    if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
+    int per = width;
+    while (per > 4 * TW_MOE_WARPS && (size_t)rows * ((width + per - 1) / per) < 592) per = (per + 1) / 2;
+    per = ((per + TW_MOE_WARPS - 1) / TW_MOE_WARPS) * TW_MOE_WARPS;
+    const dim3 grid(rows, (width + per - 1) / per);
+    if (dtype == TW_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tw_launch(moe_down_kernel<float>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (float*)out, (const float*)act,
+                         (const float*)wd, chosen, weight, (const float*)shared, shared_gate, width, F, E, top, per);
+    }
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(moe_down_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return tw_launch(moe_down_kernel<__nv_bfloat16>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)act, (const __nv_bfloat16*)wd, chosen, weight, (const __nv_bfloat16*)shared,
+                     shared_gate, width, F, E, top, per);
+}

@@ -507,17 +507,20 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, positions: torch.Tenso
                       n_tokens: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
                       status: torch.Tensor) -> None:
     """Exact paged causal attention, one block per (token, head).  q may be a column
-    slice of the packed qkv buffer (row stride is passed on)."""
+    slice of the packed qkv buffer (row stride is passed on).  The value pages may have rows of another
+    length than the key pages; the output then has heads of that length."""
     _cuda(out, q, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status)
-    _need(head_dim <= 256, f"attention: head_dim {head_dim} above 256 is not supported")
+    _need(head_dim <= 256 and v_pages.shape[3] <= 256, f"attention: head sizes above 256 are not supported")
+    _need(k_pages.shape[3] == head_dim and k_pages.shape[:3] == v_pages.shape[:3] and k_pages.is_contiguous()
+          and v_pages.is_contiguous(), "attention: pages must be contiguous [pages, kv_heads, page, head size]")
     _need(n_q_heads % n_kv_heads == 0, "attention: query heads must be a multiple of key/value heads")
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype, "attention: bad operands")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention: bad block table")
     code = _fn("attention_generic", "tw_attn_generic")(
         _ptr(out), c_int(out.stride(0)), _ptr(q), c_int(q.stride(0)), _ptr(positions), _ptr(seq_of_token),
         _ptr(seq_slot), _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_tokens),
-        c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
-        c_int(window), c_float(scale), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
+        c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_pages.shape[3]), c_int(k_pages.shape[2]),
+        c_int(k_pages.shape[0]), c_int(window), c_float(scale), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
     _check(code, "attention_generic")
 
 
@@ -1192,3 +1195,223 @@ def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: 
                                                                     prefetch.numel() * prefetch.element_size()
                                                                     if prefetch is not None else 0), _stream())
     _check(code, "gemm_tcgen05_stream")
+
+
+# ---------------------------------------------------------------------------
+# pieces of mixers that are not attention over a cache: recurrences with a matrix state, token shift
+# ---------------------------------------------------------------------------
+RECURRENCE_RETENTION, RECURRENCE_WKV, RECURRENCE_MLSTM = 0, 1, 2
+RECURRENCE_MAX_KEY_DIM = 128      # a thread keeps a column of the state in registers
+
+
+def recurrence_state_numel(mode: int, heads: int, key_dim: int, value_dim: int) -> int:
+    """fp32 values a request's state takes: per head S [Dk, Dv]; the mLSTM rule adds its normaliser as one more
+    column and its running maximum."""
+    if mode == RECURRENCE_MLSTM:
+        return heads * (key_dim * (value_dim + 1) + 1)
+    return heads * key_dim * value_dim
+
+
+def linear_recurrence(mode: int, out: torch.Tensor, den: torch.Tensor | None, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                      state: torch.Tensor, positions: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
+                      seq_q_len: torch.Tensor, n_seqs: int, heads: int, key_dim: int, value_dim: int, write_state: bool = True,
+                      pre: torch.Tensor | None = None, p0: torch.Tensor | None = None, p1: torch.Tensor | None = None,
+                      inv_freq: torch.Tensor | None = None, rot_dims: int = 0, q_scale: float = 1.0, k_scale: float = 1.0,
+                      cap: float = 1.0, tail: torch.Tensor | None = None, tail_offset: int = 0) -> None:
+    """Walk every request's rows of the step through its matrix state (csrc/linear_recurrence.cu): ``out`` fp32
+    [rows, heads * value_dim] receives the raw outputs, ``den`` fp32 [rows, heads] the mLSTM denominators.  q, k, v are
+    column slices of the projected rows (heads side by side).  ``pre``: fp32 rows the rule needs beside them (wkv:
+    the projected decay [rows, heads * key_dim]; mlstm: the gates' pre-activations [rows, 2 * heads]); ``p0`` / ``p1``
+    fp32 constants (wkv: decay offset and bonus; retention: decay per head; mlstm: gate biases).  ``tail``: rows whose
+    last one per request is copied into the state behind the heads (wkv's token shift), at ``tail_offset``."""
+    _cuda(out, den, q, k, v, state, positions, seq_slot, seq_q_start, seq_q_len, pre, p0, p1, inv_freq, tail)
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == heads * value_dim, "recurrence: out must be fp32 [rows, H * Dv]")
+    _need(q.dtype == k.dtype == v.dtype and q.stride(1) == k.stride(1) == v.stride(1) == 1, "recurrence: q, k, v of one type, unit column stride")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1, "recurrence: state must be fp32 [slots, numel]")
+    _need(0 < key_dim <= 256 and 0 < value_dim <= 256, "recurrence: head sizes must lie in 1..256")
+    for t in (pre, p0, p1, inv_freq, den):
+        _need(t is None or t.dtype == torch.float32, "recurrence: constants, gates and denominators are fp32")
+    _need(mode != RECURRENCE_MLSTM or (den is not None and pre is not None and p0 is not None), "recurrence: mlstm needs gates and a denominator buffer")
+    _need(mode != RECURRENCE_WKV or (pre is not None and p0 is not None and p1 is not None and key_dim == value_dim), "recurrence: wkv needs decay rows, offset and bonus")
+    _need(mode != RECURRENCE_RETENTION or p0 is not None, "recurrence: retention needs a decay per head")
+    code = _fn("linear_recurrence", "tw_linear_recurrence", {"TW_DK": key_dim})(
+        c_int(mode), _ptr(out), _ptr(den), _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), _ptr(v), c_int(v.stride(0)),
+        _ptr(pre), c_int(0 if pre is None else pre.stride(0)), _ptr(p0), _ptr(p1), _ptr(inv_freq), c_int(rot_dims),
+        c_float(q_scale), c_float(k_scale), c_float(cap), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(tail),
+        c_int(0 if tail is None else tail.stride(0)), c_int(0 if tail is None else tail.shape[1]), ctypes.c_longlong(tail_offset),
+        _ptr(positions), _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(heads), c_int(key_dim),
+        c_int(value_dim), c_int(1 if write_state else 0), c_int(dtype_code(q.dtype)), _stream())
+    _check(code, "linear_recurrence")
+
+
+GATE_NONE, GATE_SILU, GATE_SIGMOID = 0, 1, 2
+
+
+def head_norm_gate(out: torch.Tensor, raw: torch.Tensor, den: torch.Tensor | None, weight: torch.Tensor | None,
+                   gate: torch.Tensor | None, act: int, eps: float, n_rows: int, heads: int, value_dim: int) -> None:
+    """out[row, h] = rms_h(raw[row, h] / den[row, h]) * weight[h] * act(gate[row, h]): the norm over each head of a
+    recurrence's fp32 output, the optional weight and gate, rounded to the type of ``out``."""
+    _cuda(out, raw, den, weight, gate)
+    _need(raw.dtype == torch.float32 and raw.is_contiguous() and raw.shape[1] == heads * value_dim, "head_norm_gate: raw must be fp32 [rows, H * Dv]")
+    _need(out.stride(1) == 1 and out.shape[1] >= heads * value_dim, "head_norm_gate: bad output")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.numel() == heads * value_dim), "head_norm_gate: weight fp32 [H * Dv]")
+    _need(den is None or (den.dtype == torch.float32 and den.is_contiguous()), "head_norm_gate: den fp32 [rows, H]")
+    _need((act == GATE_NONE) == (gate is None) and (gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1)),
+          "head_norm_gate: a gate of the output's type exactly when an activation is named")
+    code = _fn("recurrent", "tw_head_norm_gate")(
+        _ptr(out), c_int(out.stride(0)), _ptr(raw), _ptr(den), _ptr(weight), _ptr(gate), c_int(0 if gate is None else gate.stride(0)),
+        c_int(act), c_float(eps), c_int(n_rows), c_int(heads), c_int(value_dim), c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "head_norm_gate")
+
+
+def token_shift_mix(out: torch.Tensor, h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, state_offset: int,
+                    seq_of_token: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor, n_rows: int) -> None:
+    """out[m, row] = h[row] + (h[row - 1] - h[row]) * mu[m] for every blend m; the row before a request's first row
+    of this step is read from the request's state (fp32 [slots, numel], ``width`` values at ``state_offset``)."""
+    _cuda(out, h, mu, state, seq_of_token, seq_slot, seq_q_start)
+    n_mix, width = mu.shape
+    _need(out.is_contiguous() and out.dim() == 3 and out.shape[0] == n_mix and out.shape[1] >= n_rows and out.shape[2] == width
+          and out.dtype == h.dtype and h.stride(1) == 1 and h.shape[1] == width, "token_shift_mix: out [mixes, rows, width] of h's type")
+    _need(mu.dtype == torch.float32 and mu.is_contiguous() and state.dtype == torch.float32 and state.stride(1) == 1,
+          "token_shift_mix: mu and state are fp32")
+    code = _fn("recurrent", "tw_token_shift_mix")(
+        _ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(h), c_int(h.stride(0)), _ptr(mu), _ptr(state),
+        ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(state_offset), _ptr(seq_of_token), _ptr(seq_slot), _ptr(seq_q_start),
+        c_int(n_rows), c_int(width), c_int(n_mix), c_int(dtype_code(h.dtype)), _stream())
+    _check(code, "token_shift_mix")
+
+
+def tanh_rows(x: torch.Tensor) -> None:
+    """tanh of every element of a contiguous tensor, in place."""
+    _cuda(x)
+    _need(x.is_contiguous(), "tanh_rows: contiguous operand")
+    code = _fn("recurrent", "tw_tanh_rows")(_ptr(x), ctypes.c_longlong(x.numel()), c_int(dtype_code(x.dtype)), _stream())
+    _check(code, "tanh_rows")
+
+
+# ---------------------------------------------------------------------------
+# hyper-connections
+# ---------------------------------------------------------------------------
+HYPER_MAX_COPIES = 8
+
+
+def hyper_step(streams: torch.Tensor, n_rows: int, init: torch.Tensor | None = None, y: torch.Tensor | None = None,
+               mix: torch.Tensor | None = None, out_coef: torch.Tensor | None = None, in_coef: torch.Tensor | None = None,
+               norm_weight: torch.Tensor | None = None, eps: float = 0.0, h_out: torch.Tensor | None = None,
+               sum_out: torch.Tensor | None = None) -> None:
+    """One pass over the copies of the residual stream (fp32 [rows, copies, width], in place), doing in this order what
+    is given: start every copy from ``init``; write a sub-layer's output ``y`` (x_t <- sum_s mix[s, t] x_s +
+    out_coef[t] y); read for the next sub-layer (``h_out`` = rmsnorm(sum_s in_coef[s] x_s) * norm_weight); sum the copies
+    into ``sum_out``."""
+    _cuda(streams, init, y, mix, out_coef, in_coef, norm_weight, h_out, sum_out)
+    _need(streams.dtype == torch.float32 and streams.is_contiguous() and streams.dim() == 3 and streams.shape[0] >= n_rows,
+          "hyper_step: the copies must be contiguous fp32 [rows, copies, width]")
+    copies, width = streams.shape[1], streams.shape[2]
+    _need(copies <= HYPER_MAX_COPIES, f"hyper_step: at most {HYPER_MAX_COPIES} copies of the stream")
+    for t, shape in ((init, (width,)), (sum_out, (width,))):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape[1:]) == shape and t.shape[0] >= n_rows),
+              "hyper_step: init and sum_out are fp32 [rows, width]")
+    _need(y is None or (mix is not None and out_coef is not None and y.is_contiguous() and y.shape[1] == width and y.shape[0] >= n_rows
+                        and mix.dtype == out_coef.dtype == torch.float32 and mix.is_contiguous() and mix.numel() == copies * copies
+                        and out_coef.numel() == copies), "hyper_step: a write needs y [rows, width], mix [copies, copies] and out_coef [copies]")
+    _need(in_coef is None or (h_out is not None and norm_weight is not None and in_coef.dtype == norm_weight.dtype == torch.float32
+                              and in_coef.numel() == copies and norm_weight.numel() == width and h_out.is_contiguous()
+                              and h_out.shape[1] == width and h_out.shape[0] >= n_rows),
+          "hyper_step: a read needs in_coef [copies], a norm weight [width] and h_out [rows, width]")
+    _need(y is None or h_out is None or y.dtype == h_out.dtype, "hyper_step: y and h_out of one type")
+    dtype = y.dtype if y is not None else (h_out.dtype if h_out is not None else torch.float32)
+    code = _fn("hyper_connections", "tw_hyper_step")(
+        _ptr(streams), _ptr(init), _ptr(y), _ptr(mix), _ptr(out_coef), _ptr(in_coef), _ptr(norm_weight), c_float(eps), _ptr(h_out),
+        _ptr(sum_out), c_int(n_rows), c_int(width), c_int(copies), c_int(dtype_code(dtype)), _stream())
+    _check(code, "hyper_step")
+
+
+# ---------------------------------------------------------------------------
+# attention mixers with keys and values of different sizes, or a position encoding no fused kernel takes
+# ---------------------------------------------------------------------------
+def add_bias_rows(rows: torch.Tensor, bias: torch.Tensor, n_rows: int) -> None:
+    """rows[:, :len(bias)] += bias, in place."""
+    _cuda(rows, bias)
+    _need(rows.stride(1) == 1 and bias.dtype == torch.float32 and bias.numel() <= rows.shape[1], "add_bias_rows: bad operands")
+    code = _fn("elementwise", "tw_add_bias_rows")(_ptr(rows), c_int(rows.stride(0)), _ptr(bias), c_int(n_rows), c_int(bias.numel()),
+                                                  c_int(dtype_code(rows.dtype)), _stream())
+    _check(code, "add_bias_rows")
+
+
+def kv_store(rows: torch.Tensor, k_col: int, v_col: int, positions: torch.Tensor, seq_of_token: torch.Tensor, seq_slot: torch.Tensor,
+             block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, n_tokens: int, status: torch.Tensor) -> None:
+    """Copy the keys (columns from ``k_col``) and values (from ``v_col``) of the step's packed rows into their pages;
+    key pages are [pages, kv_heads, page, Dk], value pages [pages, kv_heads, page, Dv]."""
+    _cuda(rows, positions, seq_of_token, seq_slot, block_table, k_pages, v_pages, status)
+    _need(rows.stride(1) == 1 and rows.dtype == k_pages.dtype == v_pages.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
+          and k_pages.shape[:3] == v_pages.shape[:3], "kv_store: pages must be contiguous and of the rows' type")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "kv_store: bad block table")
+    code = _fn("elementwise", "tw_kv_store")(
+        _ptr(rows), c_int(rows.stride(0)), c_int(k_col), c_int(v_col), _ptr(positions), _ptr(seq_of_token), _ptr(seq_slot),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), c_int(n_tokens), c_int(k_pages.shape[1]),
+        c_int(k_pages.shape[3]), c_int(v_pages.shape[3]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]),
+        c_int(dtype_code(rows.dtype)), _ptr(status), _stream())
+    _check(code, "kv_store")
+
+
+# ---------------------------------------------------------------------------
+# routed feed-forward
+# ---------------------------------------------------------------------------
+def moe_route(chosen: torch.Tensor, weight: torch.Tensor, shared_gate: torch.Tensor | None, h: torch.Tensor, w_router: torch.Tensor,
+              b_router: torch.Tensor | None, w_shared_gate: torch.Tensor | None, n_rows: int, top: int) -> None:
+    """Per row: the ``top`` experts with the largest fp32 logits ``w_router h + b_router`` (int32 [rows, top]), the
+    softmax over those logits alone (fp32 [rows, top]), and ``sigmoid(w_shared_gate . h)`` (fp32 [rows]) if asked."""
+    _cuda(chosen, weight, shared_gate, h, w_router, b_router, w_shared_gate)
+    experts, width = w_router.shape
+    _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.is_contiguous() and weight.is_contiguous()
+          and chosen.shape[1] == weight.shape[1] == top and chosen.shape[0] >= n_rows, "moe_route: chosen int32 / weight fp32 [rows, top]")
+    _need(h.stride(1) == 1 and h.shape[1] == width and h.dtype == w_router.dtype and w_router.is_contiguous() and 0 < top <= experts,
+          "moe_route: bad operands")
+    _need(b_router is None or (b_router.dtype == torch.float32 and b_router.numel() == experts), "moe_route: bias fp32 [experts]")
+    _need((w_shared_gate is None) == (shared_gate is None) and (w_shared_gate is None or (
+        w_shared_gate.dtype == h.dtype and w_shared_gate.numel() == width and w_shared_gate.is_contiguous() and shared_gate.dtype == torch.float32)),
+        "moe_route: the shared gate needs a vector of the activations' type and an fp32 output")
+    code = _fn("moe", "tw_moe_route")(_ptr(chosen), _ptr(weight), _ptr(shared_gate), _ptr(h), c_int(h.stride(0)), _ptr(w_router),
+                                      _ptr(b_router), _ptr(w_shared_gate), c_int(n_rows), c_int(width), c_int(experts), c_int(top),
+                                      c_int(dtype_code(h.dtype)), _stream())
+    _check(code, "moe_route")
+
+
+def moe_gate_up(act: torch.Tensor, h: torch.Tensor, w_gate_up: torch.Tensor, chosen: torch.Tensor, n_rows: int) -> None:
+    """act[row, j] = silu(Wg_e h[row]) * (Wu_e h[row]) for the j-th chosen expert e of the row;
+    ``w_gate_up`` is [experts, 2, ff, width] (a gate matrix followed by its up matrix)."""
+    _cuda(act, h, w_gate_up, chosen)
+    experts, two, ff, width = w_gate_up.shape
+    top = chosen.shape[1]
+    _need(two == 2 and w_gate_up.is_contiguous() and h.stride(1) == 1 and h.shape[1] == width and h.dtype == w_gate_up.dtype == act.dtype
+          and act.is_contiguous() and tuple(act.shape[1:]) == (top, ff) and act.shape[0] >= n_rows, "moe_gate_up: bad operands")
+    _need(h.dtype == torch.float32 or (w_gate_up.data_ptr() % 16 == 0), "moe_gate_up: weights must be 16-byte aligned")
+    code = _fn("moe", "tw_moe_gate_up")(_ptr(act), _ptr(h), c_int(h.stride(0)), _ptr(w_gate_up), _ptr(chosen), c_int(n_rows), c_int(width),
+                                        c_int(ff), c_int(experts), c_int(top), c_int(dtype_code(h.dtype)), _stream())
+    _check(code, "moe_gate_up")
+
+
+def moe_down(out: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
+             shared: torch.Tensor | None, shared_gate: torch.Tensor | None, n_rows: int) -> None:
+    """out[row] = sum_j weight[row, j] * Wd_e act[row, j]  (+ shared_gate[row] * shared[row]); ``w_down`` is
+    [experts, width, ff]."""
+    _cuda(out, act, w_down, chosen, weight, shared, shared_gate)
+    experts, width, ff = w_down.shape
+    top = chosen.shape[1]
+    _need(w_down.is_contiguous() and act.is_contiguous() and tuple(act.shape[1:]) == (top, ff) and out.is_contiguous()
+          and out.shape[1] == width and out.dtype == act.dtype == w_down.dtype, "moe_down: bad operands")
+    _need(shared is None or (shared.is_contiguous() and shared.dtype == out.dtype and shared.shape[1] == width), "moe_down: bad shared rows")
+    code = _fn("moe", "tw_moe_down")(_ptr(out), _ptr(act), _ptr(w_down), _ptr(chosen), _ptr(weight), _ptr(shared), _ptr(shared_gate),
+                                     c_int(n_rows), c_int(width), c_int(ff), c_int(experts), c_int(top), c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "moe_down")
+
+
+def scaled_accumulate(acc: torch.Tensor, out: torch.Tensor | None, x: torch.Tensor, scale: float, first: bool) -> None:
+    """acc = (0 if first else acc) + scale * x in fp32; ``out`` (may be None) receives the new sum in x's type."""
+    _cuda(acc, out, x)
+    _need(acc.dtype == torch.float32 and acc.is_contiguous() and x.is_contiguous() and acc.numel() == x.numel()
+          and (out is None or (out.is_contiguous() and out.dtype == x.dtype and out.numel() == x.numel())),
+          "scaled_accumulate: contiguous operands of one size, an fp32 sum")
+    code = _fn("elementwise", "tw_scaled_accumulate")(_ptr(acc), _ptr(out), _ptr(x), c_float(scale), c_int(1 if first else 0),
+                                                      ctypes.c_longlong(x.numel()), c_int(dtype_code(x.dtype)), _stream())
+    _check(code, "scaled_accumulate")

@@ -174,3 +174,108 @@ TW_EXPORT int tw_mingru_scan(void* out, int out_stride, const void* proj, int pr
                      out_stride, (const __nv_bfloat16*)proj, proj_stride, bias_z, bias_x, state, seq_slot, seq_q_start,
                      seq_q_len, width, write_state);
 }
+
+// ---------------------------------------------------------------------------
+// What follows a recurrence: per (row, head)  o = raw / den (where a denominator is given),
+// y = o / sqrt(mean(o^2) + eps) * weight * act(gate), rounded to the activation type.  One warp per (row, head).
+// act: 0 none, 1 silu, 2 sigmoid.  Everything in fp32.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(T* __restrict__ out, int out_stride, const float* __restrict__ raw, const float* __restrict__ den,
+                      const float* __restrict__ weight, const T* __restrict__ gate, int gate_stride, int act, float eps,
+                      int rows, int H, int Dv) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= rows * H) return;
+    const int row = item / H, h = item - row * H;
+    const float* r = raw + (size_t)row * H * Dv + (size_t)h * Dv;
+    const float inv_den = den ? 1.0f / den[(size_t)row * H + h] : 1.0f;
+    float ss = 0.f;
+    for (int d = lane; d < Dv; d += 32) {
+        const float o = r[d] * inv_den;
+        ss += o * o;
+    }
+    ss = tw_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)Dv + eps);
+    for (int d = lane; d < Dv; d += 32) {
+        float y = r[d] * inv_den * inv;
+        if (weight) y *= weight[h * Dv + d];
+        if (act) {
+            const float g = tw_to_float(gate[(size_t)row * gate_stride + h * Dv + d]);
+            const float sg = 1.0f / (1.0f + expf(-g));
+            y *= act == 1 ? g * sg : sg;
+        }
+        out[(size_t)row * out_stride + h * Dv + d] = tw_from_float<T>(y);
+    }
+}
+
+TW_EXPORT int tw_head_norm_gate(void* out, int out_stride, const float* raw, const float* den, const float* weight,
+                                const void* gate, int gate_stride, int act, float eps, int rows, int H, int Dv, int dtype,
+                                cudaStream_t stream) {
+    if (rows <= 0 || H <= 0) return 0;
+    const dim3 grid((unsigned)(((size_t)rows * H + 3) / 4));
+    if (dtype == TW_F32)
+        return tw_launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, 1, (float*)out, out_stride, raw, den, weight,
+                         (const float*)gate, gate_stride, act, eps, rows, H, Dv);
+    return tw_launch(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, (__nv_bfloat16*)out, out_stride, raw,
+                     den, weight, (const __nv_bfloat16*)gate, gate_stride, act, eps, rows, H, Dv);
+}
+
+// ---------------------------------------------------------------------------
+// Token shift: out[m][row] = h[row] + (h[row - 1] - h[row]) * mu[m] for `n_mix` blends of a row with the row
+// before it in the same request.  A request's first row of a step takes the row the step before left in the
+// request's state (zeros at the very first token).  fp32 arithmetic, rounded once.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_shift_mix_kernel(T* __restrict__ out, size_t mix_stride, const T* __restrict__ h, int h_stride,
+                       const float* __restrict__ mu, const float* __restrict__ state, long long state_stride,
+                       long long state_offset, const int* __restrict__ seq_of_token, const int* __restrict__ seq_slot,
+                       const int* __restrict__ seq_q_start, int width, int n_mix) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int row = blockIdx.x;
+    const int s = seq_of_token[row];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float cur = 0.f, prev = 0.f;
+        if (s >= 0) {
+            cur = tw_to_float(h[(size_t)row * h_stride + c]);
+            prev = row == seq_q_start[s] ? state[(size_t)seq_slot[s] * state_stride + state_offset + c]
+                                         : tw_to_float(h[(size_t)(row - 1) * h_stride + c]);
+        }
+        for (int m = 0; m < n_mix; ++m)
+            out[(size_t)m * mix_stride + (size_t)row * width + c] = tw_from_float<T>(cur + (prev - cur) * mu[(size_t)m * width + c]);
+    }
+}
+
+TW_EXPORT int tw_token_shift_mix(void* out, long long mix_stride, const void* h, int h_stride, const float* mu,
+                                 const float* state, long long state_stride, long long state_offset,
+                                 const int* seq_of_token, const int* seq_slot, const int* seq_q_start, int rows, int width,
+                                 int n_mix, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (dtype == TW_F32)
+        return tw_launch(token_shift_mix_kernel<float>, dim3(rows), dim3(256), 0, stream, 1, (float*)out, (size_t)mix_stride,
+                         (const float*)h, h_stride, mu, state, state_stride, state_offset, seq_of_token, seq_slot,
+                         seq_q_start, width, n_mix);
+    return tw_launch(token_shift_mix_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, 1, (__nv_bfloat16*)out,
+                     (size_t)mix_stride, (const __nv_bfloat16*)h, h_stride, mu, state, state_stride, state_offset,
+                     seq_of_token, seq_slot, seq_q_start, width, n_mix);
+}
+
+// tanh of every element, in place (the activation between the two small matrices of a projected decay).
+template <typename T>
+__global__ void tanh_rows_kernel(T* __restrict__ x, size_t count) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) x[i] = tw_from_float<T>(tanhf(tw_to_float(x[i])));
+}
+
+TW_EXPORT int tw_tanh_rows(void* x, long long count, int dtype, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const dim3 grid((unsigned)((count + 255) / 256));
+    if (dtype == TW_F32) return tw_launch(tanh_rows_kernel<float>, grid, dim3(256), 0, stream, 1, (float*)x, (size_t)count);
+    return tw_launch(tanh_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, (__nv_bfloat16*)x, (size_t)count);
+}

@@ -3,5 +3,6 @@ from .spec import LayerSpec, ModelSpec, ScheduleEntry
 from .model import Model
 from . import qwen2  # noqa: F401  (registers "Qwen2ForCausalLM")
 from . import linurax  # noqa: F401  (registers "Linurax")
+from . import sapatar  # noqa: F401  (registers "Sapatar")
 
 __all__ = ["LayerSpec", "ModelSpec", "ScheduleEntry", "Model"]

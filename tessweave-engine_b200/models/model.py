@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import FixedState, PagedKV, Runtime, StepContext, WeightDecl, build_part, join_name
+from ..parts.base import FixedState, PagedKV, Runtime, StepContext, WeightDecl, build_part, flat_needs, join_name
 from .spec import ModelSpec
 
 
@@ -25,6 +25,7 @@ class Model:
         self.head = build_part("head", spec.head, runtime, **({"tied": tied} if tied is not None else {}))
         self.graph_safe = all(p.graph_safe for p in (self.embedding, *self.blocks, self.final_norm, self.head))
         self.loaded = False
+        self.tap = None      # callable(schedule entry, stream) run behind every block: for looking at a step layer by layer
 
     # ---- weights --------------------------------------------------------
     def named_parts(self):
@@ -89,13 +90,13 @@ class Model:
     def cache_bytes_per_token(self, element_bytes: int) -> int:
         """Bytes of keys and values one token adds to the paged groups (all layers; a windowed layer
         counts like any other: the window bounds how many tokens are held, not their size)."""
-        return sum(2 * need.kv_heads * need.head_dim * element_bytes
-                   for need, _ in self.cache_needs() if isinstance(need, PagedKV))
+        return sum(need.kv_heads * (need.head_dim + need.value_dim) * element_bytes
+                   for entry, _ in self.cache_needs() for need in flat_needs(entry) if isinstance(need, PagedKV))
 
     def state_bytes_per_request(self) -> int:
         """Bytes of fixed-size state one request holds beside its pages."""
         return sum(need.numel * torch.empty((), dtype=need.dtype).element_size()
-                   for need, _ in self.cache_needs() if isinstance(need, FixedState))
+                   for entry, _ in self.cache_needs() for need in flat_needs(entry) if isinstance(need, FixedState))
 
     # ---- forward ------------------------------------------------------------
     def forward(self, ctx: StepContext, caches: list, logit_rows: torch.Tensor, n_logit_rows: int,
@@ -111,6 +112,10 @@ class Model:
         stream = self.embedding.forward(ctx)
         for i, entry in enumerate(self.spec.schedule):
             self.blocks[entry.layer].forward(ctx, stream, caches[i], write_cache=entry.cache_of is None)
+            if self.tap is not None:
+                self.tap(i, ctx, stream)
+        if stream.fold is not None:
+            stream.fold(ctx, stream)         # a block kept several copies of the stream: back to the one residual
         if n_logit_rows > 0:
             y = ctx.workspace.get("model.final", (n_logit_rows, self.spec.hidden_size), self.runtime.dtype)
             self.final_norm.apply(ctx, y, stream.resid, stream.pending, n_logit_rows, rows=logit_rows)

@@ -21,12 +21,20 @@ class GQAAttention(Mixer):
         delta   = out @ Wo.T
 
     Reference: flow_engine/model.py:36-55 (projections, packing), 183-201 (forward),
-    flow_engine/cache.py:93-100 (slots).  Weight names are the checkpoint's.
+    flow_engine/cache.py:93-100 (slots).  Weight names are the checkpoint's (``names`` replaces them).
+
+    ``v_head_dim``: the size of a value head where it differs from ``head_dim`` (the size of a query and a key
+    head); the output then has ``n_heads`` heads of that size.  Such a mixer, and one whose position encoding no
+    kernel applies on the way, adds the bias, applies the encoding and stores keys and values as separate
+    steps, and attends with the exact kernel; everything else takes the fused and tensor-core kernels.
     """
+
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+             "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias"}
 
     def __init__(self, runtime: Runtime, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  qkv_bias: bool, position: PartSpec, scale: float | None = None, window: int | None = None,
-                 out_bias: bool = False):
+                 out_bias: bool = False, v_head_dim: int | None = None, names: dict[str, str] | None = None):
         super().__init__(runtime)
         if min(hidden, n_heads, n_kv_heads, head_dim) <= 0 or n_heads % n_kv_heads:
             raise ValueError("attention: heads must be positive and n_heads a multiple of n_kv_heads")
@@ -37,26 +45,36 @@ class GQAAttention(Mixer):
         if window is not None and window <= 0:
             raise ValueError("attention: window must be positive or None")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
+        self.v_dim = head_dim if v_head_dim is None else int(v_head_dim)
+        if not 0 < self.v_dim <= 256:
+            raise ValueError(f"attention: v_head_dim {self.v_dim} must lie in 1..256")
+        self.same_dims = self.v_dim == head_dim
+        self.names = {**self.NAMES, **(names or {})}
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.window = window
         self.q_size, self.kv_size = n_heads * head_dim, n_kv_heads * head_dim
-        self.qkv_width = self.q_size + 2 * self.kv_size
+        self.v_size, self.out_size = n_kv_heads * self.v_dim, n_heads * self.v_dim
+        self.qkv_width = self.q_size + self.kv_size + self.v_size
         self.position = build_part("position", position, runtime)
         self.w_qkv = runtime.empty(self.qkv_width, hidden)
         self.b_qkv = runtime.empty(self.qkv_width, dtype=torch.float32) if qkv_bias else None
-        self.w_o = runtime.empty(hidden, self.q_size)
+        self.w_o = runtime.empty(hidden, self.out_size)
 
     def weights(self) -> list[WeightDecl]:
-        q, kv = self.q_size, self.kv_size
-        spans = (("q_proj", 0, q), ("k_proj", q, q + kv), ("v_proj", q + kv, q + 2 * kv))
-        decls = [WeightDecl(f"{n}.weight", (e - b, self.hidden), dest=self.w_qkv[b:e]) for n, b, e in spans]
+        q, kv, nm = self.q_size, self.kv_size, self.names
+        spans = (("q", 0, q), ("k", q, q + kv), ("v", q + kv, self.qkv_width))
+        decls = [WeightDecl(nm[n], (e - b, self.hidden), dest=self.w_qkv[b:e]) for n, b, e in spans]
         if self.b_qkv is not None:
-            decls += [WeightDecl(f"{n}.bias", (e - b,), role="vector", dest=self.b_qkv[b:e]) for n, b, e in spans]
-        decls.append(WeightDecl("o_proj.weight", (self.hidden, self.q_size), dest=self.w_o))
+            decls += [WeightDecl(nm[f"{n}_bias"], (e - b,), role="vector", dest=self.b_qkv[b:e]) for n, b, e in spans]
+        decls.append(WeightDecl(nm["o"], (self.hidden, self.out_size), dest=self.w_o))
         return decls
 
     def cache_need(self) -> PagedKV:
-        return PagedKV(self.n_kv_heads, self.head_dim, self.window)
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window, None if self.same_dims else self.v_dim)
+
+    def _fused_table(self):
+        """The rotation table of the kernels that rotate on the way; None where the mixer takes the separate steps."""
+        return self.position.fused_rotary_table(self.head_dim) if self.same_dims else None
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache, write_cache: bool):
         if not isinstance(cache, PagedView):
@@ -66,7 +84,7 @@ class GQAAttention(Mixer):
     def _fused_decode(self, ctx: StepContext):
         """The rotation table, if this step's attention kernel adds the bias, rotates, writes the new key and value
         and attends all by itself (decode-only steps in bfloat16 with a rotary encoding); else None."""
-        table = self.position.fused_rotary_table(self.head_dim)
+        table = self._fused_table()
         if (table is not None and ctx.decode_only and ops.fused_decode_enabled()
                 and ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim)):
             return table
@@ -76,7 +94,7 @@ class GQAAttention(Mixer):
         """h @ [Wq; Wk; Wv].T without the bias: a tensor, or the slices of a split product where the kernel
         that follows adds them itself (both rotary kernels do).  With the cache the attention will read, the
         product knows how large that launch will be and lets a small one settle on the SMs while it runs."""
-        rotary = self.position.fused_rotary_table(self.head_dim) is not None
+        rotary = self._fused_table() is not None
         fused = self._fused_decode(ctx) is not None
         early = False
         if fused and cache is not None:
@@ -110,7 +128,7 @@ class GQAAttention(Mixer):
             return None, None
         window = self.window or 0
         keys = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
-        cache_bytes = ctx.n_seqs * keys * 2 * self.n_kv_heads * self.head_dim * self.w_qkv.element_size()   # the cache has the weights' type
+        cache_bytes = ctx.n_seqs * keys * self.n_kv_heads * (self.head_dim + self.v_dim) * self.w_qkv.element_size()   # the cache has the weights' type
         first = ops.weight_prefetch_bytes() if cache_bytes >= ops.weight_prefetch_min_cache_bytes() else 0
         return (ops.weight_head(upcoming, first),
                 ops.weight_head(upcoming, ops.output_product_prefetch_bytes(), skip_bytes=first))
@@ -118,14 +136,24 @@ class GQAAttention(Mixer):
     def attend(self, ctx: StepContext, qkv, cache: PagedView, write_cache: bool) -> torch.Tensor:
         """Bias, position encoding, cache write and attention for the step's rows; [rows, Hq * D]."""
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
-        table = self.position.fused_rotary_table(self.head_dim)
+        table = self._fused_table()
         source = None
         if isinstance(qkv, SplitSum):       # the kernels below add the slices themselves
             source, qkv = qkv, ws.get("attn.qkv", (n, self.qkv_width), dt)
-        out = ws.get("attn.out", (n, self.q_size), dt)
+        out = ws.get("attn.out", (n, self.out_size), dt)
         if self._fused_decode(ctx) is not None:
             # decode-only step: the attention kernel adds the bias, rotates, writes the new key and value and attends
             self._decode(ctx, out, None, cache, fused=(source if source is not None else qkv, table, write_cache))
+            return out
+        if not self.same_dims:
+            # keys and values of different sizes: bias, the position part's own transformation, then the store
+            if self.b_qkv is not None:
+                ops.add_bias_rows(qkv, self.b_qkv, n)
+            self.position.apply(ctx, qkv, self.n_heads + self.n_kv_heads, self.head_dim)
+            if write_cache:
+                ops.kv_store(qkv, self.q_size, self.q_size + self.kv_size, ctx.positions, ctx.seq_of_token, ctx.seq_slot,
+                             cache.block_table, cache.k_pages, cache.v_pages, n, ctx.status)
+            self._attend(ctx, out, qkv, cache)
             return out
         if table is None:
             # generic path: bias, then the position part's own transformation, then the cache write
@@ -190,7 +218,7 @@ class GQAAttention(Mixer):
 
     def _attend(self, ctx: StepContext, out: torch.Tensor, qkv: torch.Tensor, cache: PagedView) -> None:
         q = qkv[:, : self.q_size]
-        if ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim):
+        if self.same_dims and ops.tensor_core_attention_supported(self.runtime.dtype, self.head_dim):
             self._attend_tensor_cores(ctx, out, q, cache)
             return
         ops.attention_generic(out, q, ctx.positions, ctx.seq_of_token, ctx.seq_slot, cache.block_table,

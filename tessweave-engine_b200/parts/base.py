@@ -70,10 +70,16 @@ class WeightDecl:
 # ---------------------------------------------------------------------------
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values for every token (or the last ``window`` tokens), in pages."""
+    """Keys and values for every token (or the last ``window`` tokens), in pages.  ``v_head_dim``: the size of
+    a value row where it differs from a key row's (``None``: the same)."""
     kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -81,6 +87,22 @@ class FixedState:
     """A state of fixed size per request (``numel`` elements of ``dtype``)."""
     numel: int
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class SeveralNeeds:
+    """What a mixer made of several mixers needs: each member's own need (``None`` for one that needs nothing),
+    in the members' order.  The cache manager answers with a ``SeveralViews`` in the same order."""
+    needs: tuple
+
+
+def flat_needs(need) -> list:
+    """The paged and fixed-size needs inside ``need``, whatever its nesting."""
+    if need is None:
+        return []
+    if isinstance(need, SeveralNeeds):
+        return [x for member in need.needs for x in flat_needs(member)]
+    return [need]
 
 
 # ---------------------------------------------------------------------------
@@ -162,6 +184,12 @@ class PagedView:
 class StateView:
     """One cache layer of fixed-size per-request state."""
     state: torch.Tensor            # [request slots, numel]
+
+
+@dataclass
+class SeveralViews:
+    """The caches of a mixer made of several mixers, one per member (``None`` where a member needs none)."""
+    views: tuple
 
 
 @dataclass
@@ -320,10 +348,10 @@ class PositionEncoding(Part):
 class Mixer(Part):
     """Mixes information between the tokens of a request (attention here)."""
 
-    def cache_need(self) -> PagedKV | FixedState | None:
+    def cache_need(self) -> PagedKV | FixedState | SeveralNeeds | None:
         return None
 
-    def forward(self, ctx: StepContext, h: torch.Tensor, cache: PagedView | StateView | None,
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: PagedView | StateView | SeveralViews | None,
                 write_cache: bool):
         """h: [n_tokens, hidden] normalised rows.  Returns the delta for the residual stream
         (a tensor or a ``SplitSum``)."""
@@ -352,10 +380,15 @@ class Block(Part):
 class ResidualStream:
     """The fp32 residual rows plus a delta (tensor or ``SplitSum``) the next norm still has to add.
     ``rounded``: the same rows (without the pending delta) in the activation type, if the part that wrote
-    them last made that copy; whoever changes ``resid`` without renewing it sets it to None."""
+    them last made that copy; whoever changes ``resid`` without renewing it sets it to None.
+    ``copies``: fp32 [rows, copies, width] when a block keeps several parallel copies of the stream instead of
+    ``resid``; such a block also sets ``fold``, which the model calls once behind the last block (and anyone who
+    wants the single stream in between) to bring ``resid`` up to date: ``fold(ctx, stream)``."""
     resid: torch.Tensor
     pending: object = None
     rounded: torch.Tensor | None = None
+    copies: torch.Tensor | None = None
+    fold: Callable | None = None
 
 
 # ---------------------------------------------------------------------------

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import FeedForward, Runtime, StepContext, WeightDecl, register_part
+from .base import FeedForward, PartSpec, Runtime, StepContext, WeightDecl, build_part, dense_delta, join_name, register_part
 from .linear import linear
 
 
@@ -82,3 +82,82 @@ class SwiGLU(FeedForward):
             gate_up = linear(ctx, "ffn.gate_up", h, self.w_gate_up)
             ops.silu_mul(act, gate_up, n, self.interleaved)
         return act
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """A mixture of gated experts, of which every token uses the ``top`` with the largest router logits.
+
+        z = Wr h + br                                  fp32
+        chosen = the `top` largest z;  c = softmax(z[chosen])
+        delta = sum_{e in chosen} c_e Wd_e (silu(Wg_e h) * (Wu_e h))   [+ sigmoid(ws . h) * shared(h)]
+
+    ``shared``: the spec of a feed-forward every token runs (its weights under ``shared_prefix``); with
+    ``shared_gate`` its output is scaled per token by sigmoid of one more dot product (tensor ``shared_gate_name``,
+    [1, hidden]).  Expert e's matrices are ``<expert_prefix><e>.gate|up|down`` in the checkpoint and live stacked:
+    gate and up as [experts, 2, ff, hidden], down as [experts, hidden, ff].  The weighted sum is fp32.
+    """
+
+    def __init__(self, runtime: Runtime, hidden: int, experts: int, top: int, intermediate: int,
+                 shared: PartSpec | None = None, shared_gate: bool = False, router_bias: bool = True,
+                 names: dict[str, str] | None = None):
+        super().__init__(runtime)
+        if min(hidden, experts, top, intermediate) <= 0 or top > experts:
+            raise ValueError("routed_experts: sizes must be positive and top at most the number of experts")
+        if shared_gate and shared is None:
+            raise ValueError("routed_experts: a gate of the shared expert needs a shared expert")
+        self.hidden, self.experts, self.top, self.intermediate = hidden, experts, top, intermediate
+        self.names = {"router": "router", "router_bias": "router.b", "expert": "e", "gate": "gate", "up": "up", "down": "down",
+                      "shared": "shared", "shared_gate": "shared.sg", **(names or {})}
+        self.w_router = runtime.empty(experts, hidden)
+        self.b_router = runtime.empty(experts, dtype=torch.float32) if router_bias else None
+        self.w_gate_up = runtime.empty(experts, 2, intermediate, hidden)
+        self.w_down = runtime.empty(experts, hidden, intermediate)
+        self.shared = build_part("feed_forward", shared, runtime) if shared is not None else None
+        self.w_shared_gate = runtime.empty(1, hidden) if shared_gate else None
+        self.graph_safe = self.shared is None or self.shared.graph_safe
+
+    def weights(self) -> list[WeightDecl]:
+        nm, f, hid = self.names, self.intermediate, self.hidden
+        decls = [WeightDecl(nm["router"], (self.experts, hid), dest=self.w_router)]
+        if self.b_router is not None:
+            decls.append(WeightDecl(nm["router_bias"], (self.experts,), role="vector", dest=self.b_router))
+        for e in range(self.experts):
+            p = f"{nm['expert']}{e}"
+            decls += [WeightDecl(join_name(p, nm["gate"]), (f, hid), dest=self.w_gate_up[e, 0]),
+                      WeightDecl(join_name(p, nm["up"]), (f, hid), dest=self.w_gate_up[e, 1]),
+                      WeightDecl(join_name(p, nm["down"]), (hid, f), dest=self.w_down[e])]
+        if self.shared is not None:
+            decls += [WeightDecl(join_name(nm["shared"], w.name), w.shape, w.role, w.init, w.dest) for w in self.shared.weights()]
+        if self.w_shared_gate is not None:
+            decls.append(WeightDecl(nm["shared_gate"], (1, hid), dest=self.w_shared_gate))
+        return decls
+
+    def finalize(self) -> None:
+        if self.shared is not None:
+            self.shared.finalize()
+
+    def streamed_first(self) -> torch.Tensor | None:
+        return None
+
+    def route(self, ctx: StepContext, h: torch.Tensor):
+        """(chosen int32 [rows, top], weights fp32 [rows, top], gate of the shared expert fp32 [rows] or None)"""
+        n, ws = ctx.n_tokens, ctx.workspace
+        chosen = ws.get("moe.chosen", (n, self.top), torch.int32)
+        weight = ws.get("moe.weight", (n, self.top), torch.float32)
+        gate = ws.get("moe.shared_gate", (n,), torch.float32) if self.w_shared_gate is not None else None
+        ops.moe_route(chosen, weight, gate, h, self.w_router, self.b_router,
+                      self.w_shared_gate.view(-1) if self.w_shared_gate is not None else None, n, self.top)
+        return chosen, weight, gate
+
+    def forward(self, ctx: StepContext, h: torch.Tensor):
+        n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
+        chosen, weight, gate = self.route(ctx, h)
+        act = ws.get("moe.act", (n, self.top, self.intermediate), dt)
+        ops.moe_gate_up(act, h, self.w_gate_up, chosen, n)
+        shared = None
+        if self.shared is not None:
+            shared = dense_delta(ctx, self.shared.forward(ctx, h), dt, "moe.shared")
+        out = ws.get("moe.delta", (n, self.hidden), dt)
+        ops.moe_down(out, act, self.w_down, chosen, weight, shared, gate, n)
+        return out

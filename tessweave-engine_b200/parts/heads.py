@@ -17,7 +17,7 @@ class LinearHead(Head):
     through the hand-written kernels; the rest is a library product.
     """
 
-    def __init__(self, runtime: Runtime, vocab: int, hidden: int, tied: torch.Tensor | None = None):
+    def __init__(self, runtime: Runtime, vocab: int, hidden: int, tied: torch.Tensor | None = None, weight_name: str = "weight"):
         super().__init__(runtime)
         if min(vocab, hidden) <= 0:
             raise ValueError("head needs a positive vocabulary and width")
@@ -25,13 +25,14 @@ class LinearHead(Head):
         if tied is not None and tuple(tied.shape) != (self.vocab, self.hidden):
             raise ValueError(f"a tied head needs a [{vocab}, {hidden}] matrix, got {tuple(tied.shape)}")
         self.tied = tied is not None
+        self.weight_name = weight_name        # may be empty: the tensor then carries the part's own name
         self.weight = tied if tied is not None else runtime.empty(self.vocab, self.hidden)
 
     def weights(self) -> list[WeightDecl]:
-        return [] if self.tied else [WeightDecl("weight", (self.vocab, self.hidden), dest=self.weight)]
+        return [] if self.tied else [WeightDecl(self.weight_name, (self.vocab, self.hidden), dest=self.weight)]
 
     def redundant_names(self) -> list[str]:
-        return ["weight"] if self.tied else []
+        return [self.weight_name] if self.tied else []
 
     def forward(self, ctx: StepContext, logits: torch.Tensor, y: torch.Tensor, n_rows: int) -> None:
         out = logits[:n_rows]

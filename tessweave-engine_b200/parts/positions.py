@@ -9,39 +9,56 @@ from .base import PositionEncoding, RotaryPlan, Runtime, StepContext, register_p
 
 @register_part("position", "rope")
 class RotaryEmbedding(PositionEncoding):
-    """Rotate-half rotary encoding over the whole head.
+    """Rotate-half rotary encoding over the whole head, or over its first ``dims`` values.
 
-    inv_freq[i] = theta ** (-(2 i) / D), angle = float(position) * inv_freq[i], pairs
-    (i, i + D/2); all in fp32 (reference: flow_engine/model.py:26-33).  The table of
-    inverse frequencies is made on the host with the reference's own expression and
-    uploaded once per head size, so the device only multiplies by the position.
+    inv_freq[i] = theta ** (-(2 i) / dims), angle = float(position) * inv_freq[i], pairs
+    (i, i + dims/2); all in fp32 (reference: flow_engine/model.py:26-33, where dims is the head size).
+    The table of inverse frequencies is made on the host with the reference's own expression and
+    uploaded once per head size, so the device only multiplies by the position.  Values of a head from
+    ``dims`` on pass unchanged; only the whole-head form has kernels that rotate on the way
+    (``fused_rotary_table``).
     """
 
-    def __init__(self, runtime: Runtime, theta: float):
+    def __init__(self, runtime: Runtime, theta: float, dims: int | None = None):
         super().__init__(runtime)
         if not theta > 0:
             raise ValueError("rope theta must be positive")
-        self.theta = float(theta)
+        if dims is not None and (dims < 0 or dims % 2):
+            raise ValueError(f"rope needs an even number of rotated dims, got {dims}")
+        self.theta, self.dims = float(theta), dims
         self._tables: dict[int, torch.Tensor] = {}
 
-    def fused_rotary_table(self, head_dim: int) -> torch.Tensor:
-        table = self._tables.get(head_dim)
+    def _table(self, dims: int) -> torch.Tensor:
+        table = self._tables.get(dims)
         if table is None:
-            if head_dim % 2:
-                raise ValueError(f"rope needs an even head_dim, got {head_dim}")
-            inv = self.theta ** (-torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim)
+            if dims % 2:
+                raise ValueError(f"rope needs an even number of rotated dims, got {dims}")
+            inv = self.theta ** (-torch.arange(0, dims, 2, dtype=torch.float32) / max(dims, 1))
             table = inv.to(self.runtime.device)
-            self._tables[head_dim] = table
+            self._tables[dims] = table
         return table
 
+    def _dims(self, head_dim: int) -> int:
+        dims = head_dim if self.dims is None else self.dims
+        if dims > head_dim:
+            raise ValueError(f"rope over {dims} dims does not fit a head of {head_dim}")
+        return dims
+
+    def fused_rotary_table(self, head_dim: int) -> torch.Tensor | None:
+        return self._table(head_dim) if self._dims(head_dim) == head_dim else None
+
     def rotary_plan(self, head_dim: int) -> RotaryPlan:
-        return RotaryPlan(self.fused_rotary_table(head_dim), head_dim, interleaved=False)
+        dims = self._dims(head_dim)
+        return RotaryPlan(self._table(dims), dims, interleaved=False)
 
     def apply(self, ctx: StepContext, qk: torch.Tensor, n_heads: int, head_dim: int) -> None:
         """Rotate ``n_heads`` heads at the start of each packed row in place (nothing else is touched).
         A mixer with a kernel that rotates on the way (``fused_rotary_table``) gets the same numbers."""
-        ops.rotate_heads(qk, None, ctx.positions, ctx.seq_of_token, self.fused_rotary_table(head_dim), ctx.n_tokens,
-                         n_heads, head_dim)
+        dims = self._dims(head_dim)
+        if dims == head_dim:
+            ops.rotate_heads(qk, None, ctx.positions, ctx.seq_of_token, self._table(dims), ctx.n_tokens, n_heads, head_dim)
+        elif dims:
+            ops.rotate_pairs(qk, ctx.positions, ctx.seq_of_token, self._table(dims), ctx.n_tokens, n_heads, head_dim, dims, False)
 
 
 @register_part("position", "rope_interleaved")
