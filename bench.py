@@ -5,6 +5,7 @@ decode through the Python entry point, prefill of 2,048 tokens, and decode at ba
     python bench.py --impl reference ...      # the unmodified reference, if it is installed
     python bench.py --kernels                 # every operation of a layer alone, with its roofline
     python bench.py --design linurax          # the Linurax decoder beside Qwen2 at equal layer sizes (a record of its own)
+    python bench.py --design sapatar          # the same for the Sapatar decoder
 
 The default run has the layer sizes of the Qwen2.5-7B-sized benchmark configuration with
 random weights (N(0, 0.02), drawn on the device), a batch of 8 and a context of 4,096 tokens.
@@ -352,9 +353,9 @@ def workload_run(name: str, layers: int | None) -> dict:
 
 
 def design_run(args, pk: dict, pk_source: str) -> dict:
-    """``--design linurax``: the Linurax decoder and the Qwen2 decoder at the layer sizes of the benchmark
+    """``--design linurax|sapatar``: that decoder and the Qwen2 decoder at the layer sizes of the benchmark
     configuration (``--layers`` of them, default 8 here), random weights: a prompt step of 2,048 tokens, decode at
-    batch 1 and ``--batch`` with ``--context`` keys, and the Linurax kernels alone."""
+    batch 1 and ``--batch`` with ``--context`` keys, and the design's own kernels alone."""
     import torch
     import tessweave_engine_b200 as tw
     from tessweave_engine_b200.engine import design_bench as db
@@ -364,9 +365,10 @@ def design_run(args, pk: dict, pk_source: str) -> dict:
     record = {"design": args.design, "layers": layers, "batch": args.batch, "context": args.context,
               "prefill_tokens": PREFILL_TOKENS, "peaks": pk, "peaks_source": pk_source, "dtype": "bf16",
               "data": "synthetic: random weights, uniform random token ids", "sizes": {}}
+    like = db.linurax_config_like if args.design == "linurax" else db.sapatar_config_like
     for name, qwen in sizes.items():
         entry = {}
-        for design, config in (("linurax", db.linurax_config_like(qwen, layers)), ("qwen2", dict(qwen, num_hidden_layers=layers))):
+        for design, config in ((args.design, like(qwen, layers)), ("qwen2", dict(qwen, num_hidden_layers=layers))):
             model = db.build(config)
             t = db.step_times(model, args.batch, args.context, PREFILL_TOKENS, PAGE_SIZE)
             for b in sorted({1, args.batch}):
@@ -375,11 +377,15 @@ def design_run(args, pk: dict, pk_source: str) -> dict:
             del model
             torch.cuda.empty_cache()
         record["sizes"][name] = entry
-    _, spec = tw.resolve(db.linurax_config_like(BENCH_CONFIG, 4))
-    rows = db.linurax_kernel_table(spec, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
+    if args.design == "linurax":
+        _, spec = tw.resolve(db.linurax_config_like(BENCH_CONFIG, 4))
+        rows = db.linurax_kernel_table(spec, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE)
+    else:
+        rows = db.sapatar_kernel_table(db.sapatar_config_like(BENCH_CONFIG, 4), args.batch, args.context, PREFILL_TOKENS,
+                                       pk["hbm_gbs"], pk["bf16_tflops"])
     _, qspec = tw.resolve(BENCH_CONFIG)
     qrows = kernel_table(qspec, args.batch, args.context, PREFILL_TOKENS, pk["hbm_gbs"], pk["bf16_tflops"], PAGE_SIZE,
-                         only=("attention", "RMSNorm"))
+                         only=("attention", "RMSNorm") if args.design == "linurax" else ("attention", "RMSNorm", "gate/up product", "down product"))
     print(format_table(rows + qrows), file=sys.stderr)
     record["kernels"] = rows
     record["qwen2_like_kernels"] = qrows
@@ -476,7 +482,7 @@ def main() -> int:
     ap.add_argument("--timeline", action="store_true",
                     help="record one decode step block by block on the device (kernels compiled with their recorder) "
                          "and print its launches in time order; for looking at, not a measurement")
-    ap.add_argument("--design", choices=["linurax"], default=None,
+    ap.add_argument("--design", choices=["linurax", "sapatar"], default=None,
                     help="another design beside the Qwen2 decoder at equal layer sizes: prompt and decode throughput of "
                          "both, and the design's own kernels with their rooflines (a record of its own; the default "
                          "workload and its JSON line are not touched)")

@@ -42,10 +42,12 @@ constexpr float NEG_INF = -INFINITY;
 
 using namespace tw_attn;
 
-// Element offset of key p's row in the cache, or -1 if p is outside [0, limit) or has no page.
-__device__ __forceinline__ long long key_offset(int p, int limit, const int* table, int table_stride, int page_size,
+// Element offset of key p's row in the cache, or -1 if p is outside [first, limit) or has no page.  Keys before
+// `first` (the start of the earliest window of the block) are seen by no row, and their pages may have been
+// given back already: they are not looked up.
+__device__ __forceinline__ long long key_offset(int p, int first, int limit, const int* table, int table_stride, int page_size,
                                                 int num_pages, int Hkv, int kvh, int* status) {
-    if (p < 0 || p >= limit) return -1;
+    if (p < first || p >= limit) return -1;
     const int blk = p / page_size;
     const int page = blk < table_stride ? table[blk] : -1;
     if (page < 0 || page >= num_pages) {
@@ -650,8 +652,8 @@ attn_prefill_kernel(bf16* __restrict__ out, int out_stride, const bf16* __restri
         const int kb = key_begin + t * PF_BN;
         long long* offs = offs_all + st * PF_BN;
         if (threadIdx.x < PF_BN)
-            offs[threadIdx.x] = key_offset(kb + threadIdx.x, key_end, table, table_stride, page_size, num_pages, Hkv,
-                                           kvh, status);
+            offs[threadIdx.x] = key_offset(kb + threadIdx.x, lo_block, key_end, table, table_stride, page_size, num_pages,
+                                           Hkv, kvh, status);
         __syncthreads();
         bf16* ks_ = stages + st * PF_STAGE;
         bf16* vs_ = ks_ + PF_BN * DP;

@@ -10,16 +10,16 @@
 // activation type once.  A block per token, the copies of a channel in registers.
 #include "common.cuh"
 
-#define TW_HC_MAX 8
+#define TW_HC_MAX 16      // the most copies; kernels are compiled for up to 4, 8 and 16
 
-template <typename T>
-__global__ void __launch_bounds__(256)
+template <typename T, int MAXC>
+__global__ void __launch_bounds__(1024)
 hyper_step_kernel(float* __restrict__ streams, const float* __restrict__ init, const T* __restrict__ y,
                   const float* __restrict__ mix, const float* __restrict__ outc, const float* __restrict__ inc,
                   const float* __restrict__ norm_w, float eps, T* __restrict__ h_out, float* __restrict__ sum_out,
                   int width, int copies) {
     extern __shared__ float su[];          // [width] the read sum, kept for the norm; then 33 floats of scratch
-    __shared__ float s_mix[TW_HC_MAX * TW_HC_MAX], s_out[TW_HC_MAX], s_in[TW_HC_MAX];
+    __shared__ float s_mix[MAXC * MAXC], s_out[MAXC], s_in[MAXC];
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int row = blockIdx.x;
@@ -32,41 +32,41 @@ hyper_step_kernel(float* __restrict__ streams, const float* __restrict__ init, c
     float* x = streams + (size_t)row * copies * width;
     float ss = 0.f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v[TW_HC_MAX];
+        float v[MAXC];
         if (init) {
             const float e = init[(size_t)row * width + c];
 #pragma unroll
-            for (int s = 0; s < TW_HC_MAX; ++s) v[s] = e;
+            for (int s = 0; s < MAXC; ++s) v[s] = e;
         } else {
 #pragma unroll
-            for (int s = 0; s < TW_HC_MAX; ++s) v[s] = s < copies ? x[(size_t)s * width + c] : 0.f;
+            for (int s = 0; s < MAXC; ++s) v[s] = s < copies ? x[(size_t)s * width + c] : 0.f;
         }
         if (y) {
             const float yc = tw_to_float(y[(size_t)row * width + c]);
-            float nv[TW_HC_MAX];
+            float nv[MAXC];
 #pragma unroll
-            for (int t = 0; t < TW_HC_MAX; ++t) {
+            for (int t = 0; t < MAXC; ++t) {
                 float acc = 0.f;
                 if (t < copies) {
 #pragma unroll
-                    for (int s = 0; s < TW_HC_MAX; ++s)
+                    for (int s = 0; s < MAXC; ++s)
                         if (s < copies) acc += s_mix[s * copies + t] * v[s];
                     acc += s_out[t] * yc;
                 }
                 nv[t] = acc;
             }
 #pragma unroll
-            for (int t = 0; t < TW_HC_MAX; ++t) v[t] = nv[t];
+            for (int t = 0; t < MAXC; ++t) v[t] = nv[t];
         }
         if (init || y) {
 #pragma unroll
-            for (int s = 0; s < TW_HC_MAX; ++s)
+            for (int s = 0; s < MAXC; ++s)
                 if (s < copies) x[(size_t)s * width + c] = v[s];
         }
         if (inc) {
             float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < TW_HC_MAX; ++s)
+            for (int s = 0; s < MAXC; ++s)
                 if (s < copies) u += s_in[s] * v[s];
             su[c] = u;
             ss += u * u;
@@ -74,7 +74,7 @@ hyper_step_kernel(float* __restrict__ streams, const float* __restrict__ init, c
         if (sum_out) {
             float t = 0.f;
 #pragma unroll
-            for (int s = 0; s < TW_HC_MAX; ++s)
+            for (int s = 0; s < MAXC; ++s)
                 if (s < copies) t += v[s];
             sum_out[(size_t)row * width + c] = t;
         }
@@ -94,14 +94,22 @@ TW_EXPORT int tw_hyper_step(float* streams, const float* init, const void* y, co
         return (int)cudaErrorInvalidValue;
     const size_t smem = ((size_t)width + 33) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    // a step of few rows is a chain of round trips to memory per thread: then a row gets a thread per channel or so
+    const int threads = rows <= 64 ? min(1024, max(256, ((width + 31) / 32) * 32)) : 256;
+#define TW_HC_LAUNCH(T, MAXC)                                                                                              \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024)                                                                                              \
+            cudaFuncSetAttribute(hyper_step_kernel<T, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+        return tw_launch(hyper_step_kernel<T, MAXC>, dim3(rows), dim3(threads), smem, stream, 1, streams, init, (const T*)y, mix, \
+                         outc, inc, norm_w, eps, (T*)h_out, sum_out, width, copies);                                       \
+    } while (0)
     if (dtype == TW_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(hyper_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return tw_launch(hyper_step_kernel<float>, dim3(rows), dim3(256), smem, stream, 1, streams, init, (const float*)y, mix,
-                         outc, inc, norm_w, eps, (float*)h_out, sum_out, width, copies);
+        if (copies <= 4) TW_HC_LAUNCH(float, 4);
+        if (copies <= 8) TW_HC_LAUNCH(float, 8);
+        TW_HC_LAUNCH(float, 16);
     }
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(hyper_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return tw_launch(hyper_step_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, stream, 1, streams, init,
-                     (const __nv_bfloat16*)y, mix, outc, inc, norm_w, eps, (__nv_bfloat16*)h_out, sum_out, width, copies);
+    if (copies <= 4) TW_HC_LAUNCH(__nv_bfloat16, 4);
+    if (copies <= 8) TW_HC_LAUNCH(__nv_bfloat16, 8);
+    TW_HC_LAUNCH(__nv_bfloat16, 16);
+#undef TW_HC_LAUNCH
 }

@@ -11,8 +11,9 @@
 //                      i = cap tanh((pi + bi) / cap), f = logsigmoid(cap tanh((pf + bf) / cap)); m is 0 before
 //                      the first token.  n is carried as one more column of S (a value that is always 1).
 //
-// One block per (head, request): thread j owns column j of S in registers (TW_DK values, a compile-time
-// size) and walks the request's rows of this step in order; the rows of 16 tokens at a time are staged in
+// One block per (head, request, slice of the columns of S): thread j owns one column of S in registers (TW_DK
+// values, a compile-time size) and walks the request's rows of this step in order (the columns of a head are
+// independent of one another, so a head is spread over as many blocks as it takes to fill the GPU); the rows of 16 tokens at a time are staged in
 // shared memory as fp32 (rotation, scaling, decays and gates are evaluated there, once per value).  The
 // state slot is read at the first row and written back after the last, so a request may be cut into
 // steps anywhere, and the sums at a position are formed in the same order however it was cut.  Outputs are
@@ -49,7 +50,7 @@ __device__ __forceinline__ float tw_logsigmoid(float x) {
 }
 
 template <typename T, int MODE>
-__global__ void __launch_bounds__(288)
+__global__ void __launch_bounds__(128)
 linear_recurrence_kernel(RecArgs a) {
     extern __shared__ float sm[];
     constexpr int DK = TW_DK, C = TW_REC_CHUNK;
@@ -60,13 +61,13 @@ linear_recurrence_kernel(RecArgs a) {
     if (len <= 0) return;
     const int start = a.seq_q_start[s];
     const int Dv = a.Dv, cols = MODE == TW_REC_MLSTM ? Dv + 1 : Dv;
-    const int j = threadIdx.x;
+    const int j = blockIdx.z * blockDim.x + threadIdx.x;
     const bool live = j < cols;
     float* sq = sm;                         // [C][DK]
     float* sk = sq + C * DK;                // [C][DK]
     float* sw = sk + C * DK;                // [C][DK] (wkv) or [C][2] gates (mlstm)
-    float* sv = sw + (MODE == TW_REC_WKV ? C * DK : (MODE == TW_REC_MLSTM ? 2 * C : 0));   // [C][Dv]
-    float* su = sv + C * Dv;                // [DK] bonus (wkv)
+    float* sv = sw + (MODE == TW_REC_WKV ? C * DK : (MODE == TW_REC_MLSTM ? 2 * C : 0));   // [C][columns of this block]
+    float* su = sv + C * blockDim.x;        // [DK] bonus (wkv)
     const long long head_state = (long long)DK * cols + (MODE == TW_REC_MLSTM ? 1 : 0);
     float* slot = a.state + (size_t)a.seq_slot[s] * a.state_stride + (size_t)h * head_state;
 
@@ -110,9 +111,9 @@ linear_recurrence_kernel(RecArgs a) {
             if (MODE == TW_REC_WKV)
                 sw[e] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
         }
-        for (int e = threadIdx.x; e < ct * Dv; e += blockDim.x) {
-            const int t = e / Dv, c = e - t * Dv;
-            sv[e] = tw_to_float(((const T*)a.v)[(size_t)(start + t0 + t) * a.v_stride + h * Dv + c]);
+        if (j < Dv) {                                    // this thread's own column of v
+            for (int t = 0; t < ct; ++t)
+                sv[t * blockDim.x + threadIdx.x] = tw_to_float(((const T*)a.v)[(size_t)(start + t0 + t) * a.v_stride + h * Dv + j]);
         }
         if (MODE == TW_REC_MLSTM) {
             for (int t = threadIdx.x; t < ct; t += blockDim.x) {
@@ -128,33 +129,66 @@ linear_recurrence_kernel(RecArgs a) {
         for (int t = 0; t < ct; ++t) {
             const float* q = sq + t * DK;
             const float* k = sk + t * DK;
-            const float vj = (MODE == TW_REC_MLSTM && j == Dv) ? 1.f : sv[t * Dv + j];
-            float acc = 0.f;
-            if (MODE == TW_REC_RETENTION) {
-#pragma unroll
-                for (int i = 0; i < DK; ++i) {
-                    S[i] = decay * S[i] + k[i] * vj;
-                    acc += q[i] * S[i];
-                }
-            } else if (MODE == TW_REC_WKV) {
-                const float* w = sw + t * DK;
-#pragma unroll
-                for (int i = 0; i < DK; ++i) {
-                    const float kv = k[i] * vj;
-                    acc += q[i] * (S[i] + su[i] * kv);
-                    S[i] = w[i] * S[i] + kv;
-                }
-            } else {
+            const float vj = (MODE == TW_REC_MLSTM && j == Dv) ? 1.f : sv[t * blockDim.x + threadIdx.x];
+            // four partial sums (key channels i mod 4), added at the end: the same order in every step, whatever its size
+            float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+            float fa = 0.f, fb = 0.f;
+            if (MODE == TW_REC_MLSTM) {
                 const float li = sw[2 * t], lf = sw[2 * t + 1];
                 const float m_new = fmaxf(lf + m, li);
-                const float fa = expf(lf + m - m_new), fb = expf(li - m_new) * vj;
+                fa = expf(lf + m - m_new);
+                fb = expf(li - m_new) * vj;
                 m = m_new;
+            }
+            const float* w = sw + t * DK;
+            if constexpr (DK % 4 == 0) {
+                const float4* q4 = reinterpret_cast<const float4*>(q);
+                const float4* k4 = reinterpret_cast<const float4*>(k);
+                const float4* w4 = reinterpret_cast<const float4*>(w);
+                const float4* u4 = reinterpret_cast<const float4*>(su);
+#pragma unroll
+                for (int i4 = 0; i4 < DK / 4; ++i4) {
+                    const float4 qq = q4[i4], kk = k4[i4];
+                    const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
+                    float wa[4] = {0.f, 0.f, 0.f, 0.f}, ua[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (MODE == TW_REC_WKV) {
+                        const float4 ww = w4[i4], uu = u4[i4];
+                        wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w;
+                        ua[0] = uu.x; ua[1] = uu.y; ua[2] = uu.z; ua[3] = uu.w;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 4 * i4 + e;
+                        if (MODE == TW_REC_RETENTION) {
+                            S[i] = decay * S[i] + ka[e] * vj;
+                            acc4[e] += qa[e] * S[i];
+                        } else if (MODE == TW_REC_WKV) {
+                            const float kv = ka[e] * vj;
+                            acc4[e] += qa[e] * (S[i] + ua[e] * kv);
+                            S[i] = wa[e] * S[i] + kv;
+                        } else {
+                            S[i] = fa * S[i] + fb * ka[e];
+                            acc4[e] += qa[e] * S[i];
+                        }
+                    }
+                }
+            } else {
 #pragma unroll
                 for (int i = 0; i < DK; ++i) {
-                    S[i] = fa * S[i] + fb * k[i];
-                    acc += q[i] * S[i];
+                    if (MODE == TW_REC_RETENTION) {
+                        S[i] = decay * S[i] + k[i] * vj;
+                        acc4[i & 3] += q[i] * S[i];
+                    } else if (MODE == TW_REC_WKV) {
+                        const float kv = k[i] * vj;
+                        acc4[i & 3] += q[i] * (S[i] + su[i] * kv);
+                        S[i] = w[i] * S[i] + kv;
+                    } else {
+                        S[i] = fa * S[i] + fb * k[i];
+                        acc4[i & 3] += q[i] * S[i];
+                    }
                 }
             }
+            const float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
             const size_t row = (size_t)(start + t0 + t);
             if (MODE == TW_REC_MLSTM && j == Dv)
                 a.den[row * a.H + h] = fmaxf(fabsf(acc), expf(-m)) + 1e-6f;
@@ -167,8 +201,8 @@ linear_recurrence_kernel(RecArgs a) {
 #pragma unroll
         for (int i = 0; i < DK; ++i) slot[(size_t)i * cols + j] = S[i];
     }
-    if (MODE == TW_REC_MLSTM && threadIdx.x == 0) slot[(size_t)DK * cols] = m;
-    if (MODE == TW_REC_WKV && h == 0 && a.tail_src) {
+    if (MODE == TW_REC_MLSTM && j == 0) slot[(size_t)DK * cols] = m;
+    if (MODE == TW_REC_WKV && h == 0 && blockIdx.z == 0 && a.tail_src) {
         // what the next step's first token mixes with: the last row this mixer read
         const T* src = (const T*)a.tail_src + (size_t)(start + len - 1) * a.tail_stride;
         float* dst = a.state + (size_t)a.seq_slot[s] * a.state_stride + a.tail_offset;
@@ -179,8 +213,11 @@ linear_recurrence_kernel(RecArgs a) {
 template <typename T, int MODE>
 static int launch_recurrence(const RecArgs& a, int n_seqs, cudaStream_t stream) {
     const int cols = MODE == TW_REC_MLSTM ? a.Dv + 1 : a.Dv;
-    const int threads = ((cols + 31) / 32) * 32;
-    size_t floats = 2 * TW_REC_CHUNK * TW_DK + (size_t)TW_REC_CHUNK * a.Dv + TW_DK;
+    // columns per block: as many as still give the GPU a block per SM, at least a warp's worth
+    int per = 128;
+    while (per > 32 && (long long)a.H * n_seqs * ((cols + per - 1) / per) < 148) per >>= 1;
+    if (per > ((cols + 31) / 32) * 32) per = ((cols + 31) / 32) * 32;
+    size_t floats = 2 * TW_REC_CHUNK * TW_DK + (size_t)TW_REC_CHUNK * per + TW_DK;
     floats += MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_DK : 2 * TW_REC_CHUNK;
     const size_t smem = floats * sizeof(float);
     if (smem > 48 * 1024) {
@@ -188,7 +225,7 @@ static int launch_recurrence(const RecArgs& a, int n_seqs, cudaStream_t stream) 
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return tw_launch(linear_recurrence_kernel<T, MODE>, dim3(a.H, n_seqs), dim3(threads), smem, stream, 1, a);
+    return tw_launch(linear_recurrence_kernel<T, MODE>, dim3(a.H, n_seqs, (cols + per - 1) / per), dim3(per), smem, stream, 1, a);
 }
 
 TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void* q, int q_stride, const void* k, int k_stride,

@@ -43,7 +43,7 @@ template <> __device__ __forceinline__ float tw_dot<__nv_bfloat16>(const __nv_bf
 }
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, float* __restrict__ shared_gate,
                  const T* __restrict__ h, int h_stride, const T* __restrict__ wr, const float* __restrict__ br,
                  const T* __restrict__ ws, int width, int E, int top) {
@@ -56,7 +56,7 @@ moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight, float* __
     for (int c = threadIdx.x; c < width; c += blockDim.x) x[c] = tw_to_float(h[(size_t)row * h_stride + c]);
     __syncthreads();
     const bool vec = (width & 7) == 0;
-    for (int e = warp; e < E + (ws ? 1 : 0); e += 4) {
+    for (int e = warp; e < E + (ws ? 1 : 0); e += (int)(blockDim.x >> 5)) {
         const float d = tw_dot<T>(e < E ? wr + (size_t)e * width : ws, x, width, lane, vec);
         if (lane == 0) z[e] = e < E ? d + (br ? br[e] : 0.f) : d;
     }
@@ -91,10 +91,11 @@ TW_EXPORT int tw_moe_route(int* chosen, float* weight, float* shared_gate, const
     if (E <= 0 || top <= 0 || top > E) return (int)cudaErrorInvalidValue;
     const size_t smem = ((size_t)width + 2 * E + 1) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const int threads = 32 * min(16, max(4, E + 1));        // a warp per expert (and one for the shared gate), up to 16
     if (dtype == TW_F32)
-        return tw_launch(moe_route_kernel<float>, dim3(rows), dim3(128), smem, stream, 1, chosen, weight, shared_gate,
+        return tw_launch(moe_route_kernel<float>, dim3(rows), dim3(threads), smem, stream, 1, chosen, weight, shared_gate,
                          (const float*)h, h_stride, (const float*)wr, br, (const float*)ws, width, E, top);
-    return tw_launch(moe_route_kernel<__nv_bfloat16>, dim3(rows), dim3(128), smem, stream, 1, chosen, weight, shared_gate,
+    return tw_launch(moe_route_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, stream, 1, chosen, weight, shared_gate,
                      (const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)wr, br, (const __nv_bfloat16*)ws, width, E, top);
 }
 
@@ -190,4 +191,106 @@ TW_EXPORT int tw_moe_down(void* out, const void* act, const void* wd, const int*
     return tw_launch(moe_down_kernel<__nv_bfloat16>, grid, dim3(32 * TW_MOE_WARPS), smem, stream, 1, (__nv_bfloat16*)out,
                      (const __nv_bfloat16*)act, (const __nv_bfloat16*)wd, chosen, weight, (const __nv_bfloat16*)shared,
                      shared_gate, width, F, E, top, per);
+}
+
+// ---------------------------------------------------------------------------
+// Steps with many rows: the (token, expert) pairs are sorted by expert, so that each expert's rows stand together
+// and its matrices meet them in one product with many rows.
+//
+//   tw_moe_sort      order[i] = the pair (token * top + j) at sorted place i; place[pair] = its place;
+//                    ends[e] = one past the last place of expert e (the prefix sum of the experts' counts)
+//   tw_moe_gather    xs[i] = h[order[i] / top]
+//   tw_moe_combine   out[token] = sum_j weight[token, j] * ys[place[token * top + j]]  (+ gate * shared[token])
+//
+// The order of the pairs inside an expert's group is whatever the atomics give; no result depends on it.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(int* __restrict__ order, int* __restrict__ place, int* __restrict__ ends, const int* __restrict__ chosen,
+                int pairs, int E) {
+    extern __shared__ int cnt[];            // [E] counts, then [E] running starts
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    int* start = cnt + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = chosen[p];
+        if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            start[e] = run;
+            run += cnt[e];
+            ends[e] = run;
+        }
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = chosen[p];
+        if (e >= 0 && e < E) {
+            const int at = atomicAdd(&start[e], 1);
+            order[at] = p;
+            place[p] = at;
+        } else {
+            place[p] = -1;
+        }
+    }
+}
+
+TW_EXPORT int tw_moe_sort(int* order, int* place, int* ends, const int* chosen, int pairs, int E, cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (E <= 0 || E > 4096) return (int)cudaErrorInvalidValue;
+    return tw_launch(moe_sort_kernel, dim3(1), dim3(1024), 2 * (size_t)E * sizeof(int), stream, 1, order, place, ends, chosen,
+                     pairs, E);
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ h, int h_stride, const int* __restrict__ order,
+                                  int top, int width) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int i = blockIdx.x;
+    const T* src = h + (size_t)(order[i] / top) * h_stride;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) xs[(size_t)i * width + c] = src[c];
+}
+
+TW_EXPORT int tw_moe_gather(void* xs, const void* h, int h_stride, const int* order, int pairs, int top, int width, int dtype,
+                            cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (dtype == TW_F32)
+        return tw_launch(moe_gather_kernel<float>, dim3(pairs), dim3(256), 0, stream, 1, (float*)xs, (const float*)h, h_stride,
+                         order, top, width);
+    return tw_launch(moe_gather_kernel<__nv_bfloat16>, dim3(pairs), dim3(256), 0, stream, 1, (__nv_bfloat16*)xs,
+                     (const __nv_bfloat16*)h, h_stride, order, top, width);
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ ys, const int* __restrict__ place,
+                                   const float* __restrict__ weight, const T* __restrict__ shared,
+                                   const float* __restrict__ shared_gate, int top, int width) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int row = blockIdx.x;
+    const float sg = shared ? (shared_gate ? shared_gate[row] : 1.f) : 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int at = place[(size_t)row * top + j];
+            if (at >= 0) acc += weight[(size_t)row * top + j] * tw_to_float(ys[(size_t)at * width + c]);
+        }
+        if (shared) acc += sg * tw_to_float(shared[(size_t)row * width + c]);
+        out[(size_t)row * width + c] = tw_from_float<T>(acc);
+    }
+}
+
+TW_EXPORT int tw_moe_combine(void* out, const void* ys, const int* place, const float* weight, const void* shared,
+                             const float* shared_gate, int rows, int top, int width, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (dtype == TW_F32)
+        return tw_launch(moe_combine_kernel<float>, dim3(rows), dim3(256), 0, stream, 1, (float*)out, (const float*)ys, place,
+                         weight, (const float*)shared, shared_gate, top, width);
+    return tw_launch(moe_combine_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, 1, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)ys, place, weight, (const __nv_bfloat16*)shared, shared_gate, top, width);
 }

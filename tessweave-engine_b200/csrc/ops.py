@@ -1201,7 +1201,7 @@ def gemm_tcgen05_stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, m: 
 # pieces of mixers that are not attention over a cache: recurrences with a matrix state, token shift
 # ---------------------------------------------------------------------------
 RECURRENCE_RETENTION, RECURRENCE_WKV, RECURRENCE_MLSTM = 0, 1, 2
-RECURRENCE_MAX_KEY_DIM = 128      # a thread keeps a column of the state in registers
+RECURRENCE_MAX_KEY_DIM = 256      # a thread keeps a column of the state in registers (beyond 128 it spills)
 
 
 def recurrence_state_numel(mode: int, heads: int, key_dim: int, value_dim: int) -> int:
@@ -1292,7 +1292,7 @@ def tanh_rows(x: torch.Tensor) -> None:
 # ---------------------------------------------------------------------------
 # hyper-connections
 # ---------------------------------------------------------------------------
-HYPER_MAX_COPIES = 8
+HYPER_MAX_COPIES = 16
 
 
 def hyper_step(streams: torch.Tensor, n_rows: int, init: torch.Tensor | None = None, y: torch.Tensor | None = None,
@@ -1415,3 +1415,38 @@ def scaled_accumulate(acc: torch.Tensor, out: torch.Tensor | None, x: torch.Tens
     code = _fn("elementwise", "tw_scaled_accumulate")(_ptr(acc), _ptr(out), _ptr(x), c_float(scale), c_int(1 if first else 0),
                                                       ctypes.c_longlong(x.numel()), c_int(dtype_code(x.dtype)), _stream())
     _check(code, "scaled_accumulate")
+
+
+def moe_sort(order: torch.Tensor, place: torch.Tensor, ends: torch.Tensor, chosen: torch.Tensor, n_rows: int) -> None:
+    """Sort the (row, chosen expert) pairs of ``chosen[:n_rows]`` by expert: ``order[i]`` = the pair at sorted place
+    i, ``place[pair]`` = its place, ``ends[e]`` = one past expert e's last place (all int32)."""
+    _cuda(order, place, ends, chosen)
+    top = chosen.shape[1]
+    pairs = n_rows * top
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (order, place, ends, chosen)) and order.numel() >= pairs
+          and place.numel() >= pairs, "moe_sort: int32 operands, one place per pair")
+    code = _fn("moe", "tw_moe_sort")(_ptr(order), _ptr(place), _ptr(ends), _ptr(chosen), c_int(pairs), c_int(ends.numel()), _stream())
+    _check(code, "moe_sort")
+
+
+def moe_gather(xs: torch.Tensor, h: torch.Tensor, order: torch.Tensor, pairs: int, top: int) -> None:
+    """xs[i] = h[order[i] // top]: every pair's input row, in sorted order."""
+    _cuda(xs, h, order)
+    _need(xs.is_contiguous() and xs.dtype == h.dtype and h.stride(1) == 1 and xs.shape[1] == h.shape[1] and xs.shape[0] >= pairs,
+          "moe_gather: bad operands")
+    code = _fn("moe", "tw_moe_gather")(_ptr(xs), _ptr(h), c_int(h.stride(0)), _ptr(order), c_int(pairs), c_int(top),
+                                       c_int(h.shape[1]), c_int(dtype_code(h.dtype)), _stream())
+    _check(code, "moe_gather")
+
+
+def moe_combine(out: torch.Tensor, ys: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, shared: torch.Tensor | None,
+                shared_gate: torch.Tensor | None, n_rows: int) -> None:
+    """out[row] = sum_j weight[row, j] * ys[place[row * top + j]]  (+ shared_gate[row] * shared[row])."""
+    _cuda(out, ys, place, weight, shared, shared_gate)
+    top, width = weight.shape[1], out.shape[1]
+    _need(out.is_contiguous() and ys.is_contiguous() and ys.dtype == out.dtype and ys.shape[1] == width and weight.is_contiguous()
+          and weight.dtype == torch.float32 and place.dtype == torch.int32, "moe_combine: bad operands")
+    _need(shared is None or (shared.is_contiguous() and shared.dtype == out.dtype and shared.shape[1] == width), "moe_combine: bad shared rows")
+    code = _fn("moe", "tw_moe_combine")(_ptr(out), _ptr(ys), _ptr(place), _ptr(weight), _ptr(shared), _ptr(shared_gate),
+                                        c_int(n_rows), c_int(top), c_int(width), c_int(dtype_code(out.dtype)), _stream())
+    _check(code, "moe_combine")

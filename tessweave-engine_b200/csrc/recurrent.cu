@@ -250,6 +250,49 @@ token_shift_mix_kernel(T* __restrict__ out, size_t mix_stride, const T* __restri
     }
 }
 
+// bf16 rows whose width is a multiple of 8: a thread blends eight neighbouring channels with 16-byte accesses.
+__global__ void __launch_bounds__(512)
+token_shift_mix_bf16x8_kernel(__nv_bfloat16* __restrict__ out, size_t mix_stride, const __nv_bfloat16* __restrict__ h, int h_stride,
+                              const float* __restrict__ mu, const float* __restrict__ state, long long state_stride,
+                              long long state_offset, const int* __restrict__ seq_of_token, const int* __restrict__ seq_slot,
+                              const int* __restrict__ seq_q_start, int width, int n_mix) {
+    tw_grid_wait();
+    tw_grid_launch_dependents();
+    const int row = blockIdx.x;
+    const int s = seq_of_token[row];
+    for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+        float cur[8], prev[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) cur[e] = prev[e] = 0.f;
+        if (s >= 0) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(h + (size_t)row * h_stride + c);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(p2[e]); cur[2 * e] = f.x; cur[2 * e + 1] = f.y; }
+            if (row == seq_q_start[s]) {
+                const float* st = state + (size_t)seq_slot[s] * state_stride + state_offset + c;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) prev[e] = st[e];
+            } else {
+                const uint4 rawp = *reinterpret_cast<const uint4*>(h + (size_t)(row - 1) * h_stride + c);
+                const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&rawp);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(q2[e]); prev[2 * e] = f.x; prev[2 * e + 1] = f.y; }
+            }
+        }
+        for (int m = 0; m < n_mix; ++m) {
+            const float* mr = mu + (size_t)m * width + c;
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                o2[e] = __floats2bfloat162_rn(cur[2 * e] + (prev[2 * e] - cur[2 * e]) * mr[2 * e],
+                                              cur[2 * e + 1] + (prev[2 * e + 1] - cur[2 * e + 1]) * mr[2 * e + 1]);
+            *reinterpret_cast<uint4*>(out + (size_t)m * mix_stride + (size_t)row * width + c) = o;
+        }
+    }
+}
+
 TW_EXPORT int tw_token_shift_mix(void* out, long long mix_stride, const void* h, int h_stride, const float* mu,
                                  const float* state, long long state_stride, long long state_offset,
                                  const int* seq_of_token, const int* seq_slot, const int* seq_q_start, int rows, int width,
@@ -259,6 +302,13 @@ TW_EXPORT int tw_token_shift_mix(void* out, long long mix_stride, const void* h,
         return tw_launch(token_shift_mix_kernel<float>, dim3(rows), dim3(256), 0, stream, 1, (float*)out, (size_t)mix_stride,
                          (const float*)h, h_stride, mu, state, state_stride, state_offset, seq_of_token, seq_slot,
                          seq_q_start, width, n_mix);
+    if ((width & 7) == 0 && (h_stride & 7) == 0 && (mix_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        const int threads = min(512, ((width / 8 + 31) / 32) * 32);
+        return tw_launch(token_shift_mix_bf16x8_kernel, dim3(rows), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out,
+                         (size_t)mix_stride, (const __nv_bfloat16*)h, h_stride, mu, state, state_stride, state_offset,
+                         seq_of_token, seq_slot, seq_q_start, width, n_mix);
+    }
     return tw_launch(token_shift_mix_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, 1, (__nv_bfloat16*)out,
                      (size_t)mix_stride, (const __nv_bfloat16*)h, h_stride, mu, state, state_stride, state_offset,
                      seq_of_token, seq_slot, seq_q_start, width, n_mix);

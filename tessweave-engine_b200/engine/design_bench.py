@@ -198,3 +198,136 @@ def linurax_kernel_table(spec, batch: int, context: int, prefill_tokens: int, hb
     if int(status) != 0:
         raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
     return rows
+
+
+# ---------------------------------------------------------------------------
+# the Sapatar decoder
+# ---------------------------------------------------------------------------
+def sapatar_config_like(qwen: dict, layers: int) -> dict:
+    """A Sapatar config.json with the sizes of the Qwen2 configuration ``qwen``: layers [attention beside mLSTM, wkv,
+    retention, attention beside mLSTM] in turn, each with eight experts of a quarter of the dense feed-forward's size
+    (two chosen) and a shared expert of that size, four copies of the residual stream.  The attention has Qwen2's
+    head counts and head size (keys and values alike) and a window of 1,024; mLSTM and retention have half as many
+    heads of the same size; wkv has heads of 64."""
+    heads, kv, dim, width = qwen["num_attention_heads"], qwen["num_key_value_heads"], qwen["head_dim"], qwen["hidden_size"]
+    ff = qwen["intermediate_size"] // 4
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": 8, "top": 2}, "shared": {"ff": ff}}
+    rot = {"dims": dim, "base": qwen["rope_theta"]}
+    half = max(1, heads // 2)
+    parallel = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": 1024}, "rot": rot},
+        "right": {"heads": half, "dim": dim, "vdim": dim, "gate_cap": 15.0}, "left_scale": 1.0, "right_scale": 1.0}}
+    wkv = {"type": "wkv", "mlp": mlp, "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}}
+    retention = {"type": "retention", "mlp": mlp, "mixer": {"heads": half, "dim": dim, "vdim": dim, "rot": rot,
+                                                            "decay": [1.0 - 2.0 ** -(5 + h % 8) for h in range(half)]}}
+    pattern = [parallel, wkv, retention, parallel]
+    return {"architecture": "Sapatar", "vocab": qwen["vocab_size"], "width": width, "norm": {"eps": qwen["rms_norm_eps"]},
+            "streams": 4, "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def sapatar_kernel_table(config: dict, batch: int, context: int, prefill_tokens: int, hbm_gbs: float, tflops: float) -> list[dict]:
+    """The Sapatar kernels alone, each inside a CUDA graph with operands rotated beyond L2, for a decode step of
+    ``batch`` rows and a prompt step: the pass over the stream's copies, the token shift, the three recurrences, the
+    norm over heads with its gate, and the routed experts (router, and the experts' products).
+    fraction = max(bytes / HBM peak, FLOPs / tensor peak) / time."""
+    import tessweave_engine_b200 as tw
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    rt = Runtime(dev, bf)
+    cfg, _ = tw.resolve(config)
+    W, S = cfg.width, cfg.streams or 1
+    par = next(l.mixer for l in cfg.layers if l.type == "parallel")
+    wk = next(l.mixer for l in cfg.layers if l.type == "wkv")
+    ret = next(l.mixer for l in cfg.layers if l.type == "retention")
+    mlp = next(l.mlp for l in cfg.layers if l.mlp is not None)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rows: list[dict] = []
+
+    def add(name, m, thunks, nbytes, flops, reps=4, note=""):
+        kernel = _kernels_of(thunks[0])
+        us = _graph_us(thunks, reps)
+        floor = max(nbytes / (hbm_gbs * 1e9), flops / (tflops * 1e12)) * 1e6
+        rows.append({"op": name, "rows": m, "kernel": kernel, "us": round(us, 2), "mbytes": round(nbytes / 1e6, 2),
+                     "gflop": round(flops / 1e9, 2), "floor_us": round(floor, 2), "frac": round(floor / us, 3),
+                     "bound": "hbm" if nbytes / (hbm_gbs * 1e9) >= flops / (tflops * 1e12) else "tensor", "note": note})
+
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)     # noqa: E731
+    for m, phase in ((batch, "decode"), (prefill_tokens, "prefill")):
+        requests = batch if phase == "decode" else 1
+        per = m // requests
+        slots, starts, lens = i32(list(range(requests))), i32([r * per for r in range(requests)]), i32([per] * requests)
+        seq_of = i32([r for r in range(requests) for _ in range(per)])
+        positions = i32([context - 1] * m if phase == "decode" else list(range(m)))
+        # ---- the copies of the stream: write a sub-layer's output, read the next one's input through its norm
+        sets = [(torch.randn(m, S, W, device=dev), torch.randn(m, W, device=dev, dtype=bf), torch.empty(m, W, device=dev, dtype=bf))
+                for _ in range(_copies(m * W * (8 * S + 4)))]
+        mix, oc, ic, nw = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.ones(S, device=dev), torch.ones(W, device=dev)
+        add(f"{phase}: write into {S} copies of the stream + read + RMSNorm", m,
+            [(lambda x=x, y=y, h=h: ops.hyper_step(x, m, y=y, mix=mix, out_coef=oc, in_coef=ic, norm_weight=nw, eps=1e-6, h_out=h))
+             for x, y, h in sets], m * W * (8 * S + 4), 0.0, reps=8)
+        del sets
+        # ---- token shift
+        state = torch.zeros(requests, W, device=dev)
+        mu = torch.rand(5, W, device=dev)
+        sets = [(torch.randn(m, W, device=dev, dtype=bf), torch.empty(5, m, W, device=dev, dtype=bf)) for _ in range(_copies(m * W * 12))]
+        add(f"{phase}: token shift, five blends", m,
+            [(lambda h=h, o=o: ops.token_shift_mix(o, h, mu, state, 0, seq_of, slots, starts, m)) for h, o in sets], m * W * 12, 0.0, reps=8)
+        del sets
+        # ---- the three recurrences and what follows them
+        for rule, name, H, Dk, Dv in ((ops.RECURRENCE_WKV, "wkv", wk.heads, wk.dim, wk.dim),
+                                      (ops.RECURRENCE_RETENTION, "retention", ret.heads, ret.dim, ret.vdim),
+                                      (ops.RECURRENCE_MLSTM, "mlstm", par.right.heads, par.right.dim, par.right.vdim)):
+            numel = ops.recurrence_state_numel(rule, H, Dk, Dv)
+            n_sets = _copies(max(requests * numel * 8, m * H * (2 * Dk + Dv) * 2))
+            sets = []
+            for _ in range(n_sets):
+                q, k, v = (torch.randn(m, H * d, device=dev, dtype=bf) * 0.3 for d in (Dk, Dk, Dv))
+                sets.append((q, k, v, torch.zeros(requests, numel, device=dev), torch.empty(m, H * Dv, device=dev),
+                             torch.empty(m, H, device=dev)))
+            extra = {}
+            if rule == ops.RECURRENCE_WKV:
+                extra = {"pre": torch.randn(m, H * Dk, device=dev), "p0": torch.zeros(H * Dk, device=dev), "p1": torch.zeros(H * Dk, device=dev)}
+            elif rule == ops.RECURRENCE_RETENTION:
+                extra = {"p0": torch.full((H,), 0.97, device=dev), "k_scale": Dk ** -0.5,
+                         "inv_freq": torch.rand(Dk // 2, device=dev), "rot_dims": Dk}
+            else:
+                extra = {"pre": torch.randn(m, 2 * H, device=dev), "p0": torch.zeros(2 * H, device=dev), "q_scale": Dk ** -0.5, "cap": 15.0}
+            nbytes = m * H * (2 * Dk + Dv) * 2 + m * H * Dv * 4 + 2 * requests * numel * 4 + (m * H * Dk * 4 if rule == ops.RECURRENCE_WKV else 0)
+            add(f"{phase}: {name} recurrence, {H} heads of {Dk} x {Dv}", m,
+                [(lambda s=s: ops.linear_recurrence(rule, s[4], s[5] if rule == ops.RECURRENCE_MLSTM else None, s[0], s[1], s[2], s[3],
+                                                    positions, slots, starts, lens, requests, H, Dk, Dv, True, **extra)) for s in sets],
+                nbytes, 0.0, reps=2 if phase == "prefill" else 8,
+                note=f"{4.0 * m * H * Dk * Dv / 1e9:.2f} GFLOP of fp32 multiply-adds outside the tensor cores")
+            del sets
+        H, Dv = par.right.heads, par.right.vdim
+        sets = [(torch.randn(m, H * Dv, device=dev), torch.rand(m, H, device=dev) + 0.5, torch.randn(m, H * Dv, device=dev, dtype=bf),
+                 torch.empty(m, H * Dv, device=dev, dtype=bf)) for _ in range(_copies(m * H * Dv * 8))]
+        nw2 = torch.ones(H * Dv, device=dev)
+        add(f"{phase}: norm over each head + gate", m,
+            [(lambda r=r, d=d, g=g, o=o: ops.head_norm_gate(o, r, d, nw2, g, ops.GATE_SIGMOID, 1e-6, m, H, Dv)) for r, d, g, o in sets],
+            m * H * Dv * 8, 0.0, reps=8)
+        del sets
+        # ---- routed experts (without the shared expert, which is the dense feed-forward part)
+        spec = tw.PartSpec("routed_experts", {"hidden": W, "experts": mlp.experts, "top": mlp.top, "intermediate": mlp.ff})
+        part_bytes = mlp.experts * 3 * mlp.ff * W * 2
+        parts = []
+        for _ in range(_copies(part_bytes) if phase == "decode" else 2):
+            part = build_part("feed_forward", spec, rt)
+            _fill(part)
+            part.w_router.normal_(0, 0.5)
+            parts.append(part)
+        ws = Workspace(dev)
+        ctx = _context(rt, ws, status, positions.tolist(), seq_of.tolist(), list(range(requests)), starts.tolist(), lens.tolist(),
+                       [context] * requests if phase == "decode" else [m])
+        hs = [torch.randn(m, W, device=dev, dtype=bf) for _ in range(4)]
+        touched = min(mlp.experts, m * mlp.top)
+        add(f"{phase}: router, {mlp.experts} experts, {mlp.top} chosen", m,
+            [(lambda p=p, i=i: p.route(ctx, hs[i % 4])) for i, p in enumerate(parts)], m * W * 2 + mlp.experts * W * 2, 0.0, reps=8)
+        add(f"{phase}: the chosen experts' gate/up, SiLU.mul, down and the weighted sum", m,
+            [(lambda p=p, i=i: p.forward(ctx, hs[i % 4])) for i, p in enumerate(parts)],
+            touched * 3 * mlp.ff * W * 2 + m * W * 4, 2.0 * m * mlp.top * 3 * mlp.ff * W, reps=2,
+            note="includes the router; bytes: the matrices of the experts a step of this size touches at most, once")
+        del parts
+        torch.cuda.empty_cache()
+    if int(status) != 0:
+        raise RuntimeError(f"a kernel reported status {int(status)} during the kernel table")
+    return rows

@@ -179,7 +179,9 @@ class GQAAttention(Mixer):
             # long portions: tcgen05 kernel (TMA, accumulators in tensor memory); short ones, and the shapes it
             # does not take, stay on the mma.sync kernel, which starts faster
             prefill = ops.attention_prefill
-            if ops.prefer_tcgen05_attention(self.runtime.dtype, self.head_dim, cache.k_pages.shape[2], ctx.max_q_len):
+            # (not with a window: that kernel copies whole key tiles, and the pages of a tile's keys before the
+            # earliest window may have been given back; the mma.sync kernel skips such keys one by one)
+            if not window and ops.prefer_tcgen05_attention(self.runtime.dtype, self.head_dim, cache.k_pages.shape[2], ctx.max_q_len):
                 prefill = ops.attention_prefill_tcgen05
             prefill(out, q, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, ctx.seq_slot,
                                   cache.block_table, cache.k_pages, cache.v_pages, ctx.n_seqs, ctx.max_q_len,

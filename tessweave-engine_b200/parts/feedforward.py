@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, PartSpec, Runtime, StepContext, WeightDecl, build_part, dense_delta, join_name, register_part
-from .linear import linear
+from .linear import grouped_matmul_nt, linear
 
 
 @register_part("feed_forward", "swiglu")
@@ -96,7 +96,13 @@ class RoutedExperts(FeedForward):
     ``shared_gate`` its output is scaled per token by sigmoid of one more dot product (tensor ``shared_gate_name``,
     [1, hidden]).  Expert e's matrices are ``<expert_prefix><e>.gate|up|down`` in the checkpoint and live stacked:
     gate and up as [experts, 2, ff, hidden], down as [experts, hidden, ff].  The weighted sum is fp32.
+
+    Steps with few rows run each (token, expert) pair as matrix-vector products that stream the chosen experts'
+    matrices (csrc/moe.cu).  bfloat16 steps with more than ``GROUPED_MIN_ROWS`` rows sort the pairs by expert and
+    run every expert's rows through one library product with many rows, whose group bounds stay on the device.
     """
+
+    GROUPED_MIN_ROWS = 16
 
     def __init__(self, runtime: Runtime, hidden: int, experts: int, top: int, intermediate: int,
                  shared: PartSpec | None = None, shared_gate: bool = False, router_bias: bool = True,
@@ -153,11 +159,42 @@ class RoutedExperts(FeedForward):
     def forward(self, ctx: StepContext, h: torch.Tensor):
         n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
         chosen, weight, gate = self.route(ctx, h)
-        act = ws.get("moe.act", (n, self.top, self.intermediate), dt)
-        ops.moe_gate_up(act, h, self.w_gate_up, chosen, n)
         shared = None
         if self.shared is not None:
             shared = dense_delta(ctx, self.shared.forward(ctx, h), dt, "moe.shared")
         out = ws.get("moe.delta", (n, self.hidden), dt)
+        # both ways' buffers are asked for in every step, so that the workspace has its final size after the largest one
+        act = ws.get("moe.act", (n, self.top, self.intermediate), dt)
+        sorted_buffers = self._sorted_buffers(ctx)
+        if self.grouped_for(n):
+            self._grouped(ctx, h, chosen, weight, shared, gate, out, sorted_buffers)
+            return out
+        ops.moe_gate_up(act, h, self.w_gate_up, chosen, n)
         ops.moe_down(out, act, self.w_down, chosen, weight, shared, gate, n)
         return out
+
+    def grouped_for(self, n_rows: int) -> bool:
+        """Whether a step of ``n_rows`` rows sorts its pairs by expert: bfloat16, more than ``GROUPED_MIN_ROWS`` rows, and
+        rows of the matrices that start on 16-byte boundaries (the library's grouped product wants that)."""
+        return (self.runtime.dtype == torch.bfloat16 and n_rows > self.GROUPED_MIN_ROWS and self.hidden % 8 == 0
+                and self.intermediate % 8 == 0)
+
+    def _sorted_buffers(self, ctx: StepContext):
+        n, ws, dt = ctx.n_tokens, ctx.workspace, self.runtime.dtype
+        pairs = n * self.top
+        return (ws.get("moe.order", (pairs,), torch.int32), ws.get("moe.place", (pairs,), torch.int32),
+                ws.get("moe.ends", (self.experts,), torch.int32), ws.get("moe.sorted_rows", (pairs, self.hidden), dt),
+                ws.get("moe.sorted_act", (pairs, self.intermediate), dt))
+
+    def _grouped(self, ctx: StepContext, h, chosen, weight, shared, gate, out, buffers) -> None:
+        """The pairs sorted by expert; gate/up, SiLU.mul and down as products over each expert's rows; the weighted
+        sum (and the shared expert) per token."""
+        n = ctx.n_tokens
+        pairs = n * self.top
+        order, place, ends, xs, act = buffers
+        ops.moe_sort(order, place, ends, chosen, n)
+        ops.moe_gather(xs, h, order, pairs, self.top)
+        gate_up = grouped_matmul_nt(xs, self.w_gate_up.view(self.experts, 2 * self.intermediate, self.hidden), ends)
+        ops.silu_mul(act, gate_up, pairs, False)
+        ys = grouped_matmul_nt(act, self.w_down, ends)
+        ops.moe_combine(out, ys, place, weight, shared, gate, n)

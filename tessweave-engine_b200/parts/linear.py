@@ -104,3 +104,33 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
         ops.gemm_small_m(out, x, w, m, early_dependents=consumer_early, prefetch=prefetch)
         return out
     return matmul_nt(ctx.workspace.get(name, (m, n), dtype), x, w)
+
+
+_grouped_library: list = [None]     # True / False once the library's grouped product has been tried
+
+
+def grouped_matmul_nt(x: torch.Tensor, w: torch.Tensor, ends: torch.Tensor) -> torch.Tensor:
+    """Rows of ``x`` in groups that stand together (group e = rows ends[e - 1] .. ends[e] - 1, ``ends`` int32 on the
+    device), each group times its own matrix: out[i] = x[i] @ w[e(i)].T with ``w`` [groups, out, in].  bfloat16
+    operands, fp32 accumulation, a library product: one grouped launch that reads the group bounds on the device
+    where the library has it (``torch._grouped_mm``), else one product per group after the bounds have been read
+    on the host.  Rows behind the last group are left as they are."""
+    if not _configured:
+        configure_matmul_precision()
+    ops.note_call("library grouped product")
+    if _grouped_library[0] is not False and hasattr(torch, "_grouped_mm"):
+        try:
+            out = torch._grouped_mm(x, w.transpose(-2, -1), offs=ends)
+            _grouped_library[0] = True
+            return out
+        except (RuntimeError, NotImplementedError):
+            if _grouped_library[0]:
+                raise
+            _grouped_library[0] = False
+    out = torch.empty(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+    begin = 0
+    for e, end in enumerate(ends.tolist()):
+        if end > begin:
+            torch.mm(x[begin:end], w[e].t(), out=out[begin:end])
+        begin = end
+    return out

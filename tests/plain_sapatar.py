@@ -226,3 +226,42 @@ def forward(cfg, w, tokens, return_layers=False):
     logits = rms(x, w["final.norm"], eps) @ w["head"].T
     assert logits.dtype == dtype
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+# ---------------------------------------------------------------------------
+# model folders
+# ---------------------------------------------------------------------------
+def read_folder(folder, dtype=torch.float32):
+    """config.json and every tensor of model.safetensors, read with nothing but struct-like slicing and torch."""
+    import json
+    from pathlib import Path
+    folder = Path(folder)
+    config = json.loads((folder / "config.json").read_text())
+    raw = (folder / "model.safetensors").read_bytes()
+    n = int.from_bytes(raw[:8], "little")
+    header = json.loads(raw[8:8 + n])
+    kinds = {"BF16": torch.bfloat16, "F32": torch.float32, "I32": torch.int32}
+    weights = {}
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = meta["data_offsets"]
+        t = torch.frombuffer(bytearray(raw[8 + n + lo:8 + n + hi]), dtype=kinds[meta["dtype"]]).view(meta["shape"])
+        weights[name] = t.to(dtype) if t.is_floating_point() else t
+    return config, weights
+
+
+def logits_of(folder, tokens, dtype=torch.float64) -> torch.Tensor:
+    config, weights = read_folder(folder, dtype)
+    return forward(config, weights, tokens).float()
+
+
+def greedy(folder, prompt, steps):
+    """Greedy continuation, the slow way: the whole sequence again for every token (lowest index at a tie)."""
+    config, weights = read_folder(folder, torch.float64)
+    tokens, out = list(prompt), []
+    for _ in range(steps):
+        nxt = int(torch.argmax(forward(config, weights, tokens)[-1]))
+        out.append(nxt)
+        tokens.append(nxt)
+    return out

@@ -140,3 +140,54 @@ def test_generate_linurax_as_a_user_starts_it(tmp_path):
     assert proc.returncode == 0, proc.stderr[-3000:]
     got = [int(t) for t in proc.stdout.strip().split(",")]
     assert got == plain_linurax.greedy(folder, prompt, 8)
+
+
+# ---------------------------------------------------------------------------
+# the Sapatar decoder through the same command line
+# ---------------------------------------------------------------------------
+def test_doctor_and_inspect_know_sapatar(tmp_path):
+    from tiny_sapatar import SAPATAR_A
+    assert "Sapatar" in json.loads(run_cli("doctor").stdout)["architectures"]
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(SAPATAR_A))
+    folder = tmp_path / "model"
+    assert run_cli("init", folder, "--config", config, "--seed", 2, "--init-std", 0.1).returncode == 0
+    proc = run_cli("inspect", folder, "--kv-blocks", 10, "--block-size", 8)
+    assert proc.returncode == 0, proc.stderr
+    out = json.loads(proc.stdout)
+    lefts = [l["mixer"]["left"] for l in SAPATAR_A["layers"] if l["type"] == "parallel"]
+    per_token = sum(m["kv_heads"] * (m["dim"] + m["vdim"]) for m in lefts)          # keys and values of different sizes
+    assert out["kv_bf16_bytes"] == per_token * 2 * 10 * 8 and out["layers_in_schedule"] == len(SAPATAR_A["layers"])
+    states = 0
+    for layer in SAPATAR_A["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "wkv":
+            states += m["heads"] * m["dim"] * m["dim"] + SAPATAR_A["width"]
+        elif layer["type"] == "retention":
+            states += m["heads"] * m["dim"] * m["vdim"]
+        else:
+            states += m["right"]["heads"] * (m["right"]["dim"] * (m["right"]["vdim"] + 1) + 1)
+    assert out["state_bytes_per_request"] == 4 * states
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps({**SAPATAR_A, "layers": [{**SAPATAR_A["layers"][0], "type": "conv"}]}))
+    proc = run_cli("inspect", bad)
+    assert proc.returncode != 0 and "not implemented" in proc.stderr
+
+
+@pytest.mark.gpu
+def test_generate_sapatar_as_a_user_starts_it(tmp_path):
+    """init -> generate --prompt-ids in float32 -> the plain implementation's greedy continuation."""
+    import plain_sapatar
+    from tiny_sapatar import SAPATAR_D
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(SAPATAR_D))
+    folder = tmp_path / "model"
+    assert run_cli("init", folder, "--config", config, "--seed", 11, "--init-std", 0.2).returncode == 0
+    prompt = [5, 17, 3, 20, 41, 7, 50, 10, 23]
+    proc = run_cli("generate", folder, "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32", "--max-tokens", 8,
+                   "--ignore-eos", "--log", tmp_path / "runs" / "engine.jsonl", "--block-size", 8, "--kv-blocks", 32,
+                   "--prefill-chunk", 4, "--max-context", 256)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    got = [int(t) for t in proc.stdout.strip().split(",")]
+    assert got == plain_sapatar.greedy(folder, prompt, 8)
