@@ -12,8 +12,8 @@
 
 #define TW_HC_MAX 16      // the most copies; kernels are compiled for up to 4, 8 and 16
 
-template <typename T, int MAXC>
-__global__ void __launch_bounds__(1024)
+template <typename T, int MAXC, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 hyper_step_kernel(float* __restrict__ streams, const float* __restrict__ init, const T* __restrict__ y,
                   const float* __restrict__ mix, const float* __restrict__ outc, const float* __restrict__ inc,
                   const float* __restrict__ norm_w, float eps, T* __restrict__ h_out, float* __restrict__ sum_out,
@@ -96,12 +96,17 @@ TW_EXPORT int tw_hyper_step(float* streams, const float* init, const void* y, co
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     // a step of few rows is a chain of round trips to memory per thread: then a row gets a thread per channel or so
     const int threads = rows <= 64 ? min(1024, max(256, ((width + 31) / 32) * 32)) : 256;
-#define TW_HC_LAUNCH(T, MAXC)                                                                                              \
+#define TW_HC_LAUNCH_T(T, MAXC, THREADS)                                                                                   \
     do {                                                                                                                   \
         if (smem > 48 * 1024)                                                                                              \
-            cudaFuncSetAttribute(hyper_step_kernel<T, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-        return tw_launch(hyper_step_kernel<T, MAXC>, dim3(rows), dim3(threads), smem, stream, 1, streams, init, (const T*)y, mix, \
-                         outc, inc, norm_w, eps, (T*)h_out, sum_out, width, copies);                                       \
+            cudaFuncSetAttribute(hyper_step_kernel<T, MAXC, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return tw_launch(hyper_step_kernel<T, MAXC, THREADS>, dim3(rows), dim3(threads), smem, stream, 1, streams, init,   \
+                         (const T*)y, mix, outc, inc, norm_w, eps, (T*)h_out, sum_out, width, copies);                     \
+    } while (0)
+#define TW_HC_LAUNCH(T, MAXC)                                                                                              \
+    do {                                                                                                                   \
+        if (threads > 256) TW_HC_LAUNCH_T(T, MAXC, 1024);                                                                  \
+        TW_HC_LAUNCH_T(T, MAXC, 256);                                                                                      \
     } while (0)
     if (dtype == TW_F32) {
         if (copies <= 4) TW_HC_LAUNCH(float, 4);
@@ -112,4 +117,5 @@ TW_EXPORT int tw_hyper_step(float* streams, const float* init, const void* y, co
     if (copies <= 8) TW_HC_LAUNCH(__nv_bfloat16, 8);
     TW_HC_LAUNCH(__nv_bfloat16, 16);
 #undef TW_HC_LAUNCH
+#undef TW_HC_LAUNCH_T
 }

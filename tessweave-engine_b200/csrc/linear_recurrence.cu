@@ -13,7 +13,8 @@
 //
 // One block per (head, request, slice of the columns of S): thread j owns one column of S in registers (TW_DK
 // values, a compile-time size) and walks the request's rows of this step in order (the columns of a head are
-// independent of one another, so a head is spread over as many blocks as it takes to fill the GPU); the rows of 16 tokens at a time are staged in
+// independent of one another, so a head is spread over as many blocks as it takes to fill the GPU; in steps with
+// long portions the block's other warps stage the next 16 tokens meanwhile); the rows of 16 tokens at a time are staged in
 // shared memory as fp32 (rotation, scaling, decays and gates are evaluated there, once per value).  The
 // state slot is read at the first row and written back after the last, so a request may be cut into
 // steps anywhere, and the sums at a position are formed in the same order however it was cut.  Outputs are
@@ -43,6 +44,7 @@ struct RecArgs {
     const int* positions;
     const int* seq_slot; const int* seq_q_start; const int* seq_q_len;
     int H, Dv, write_state;
+    int cols_per_block;         // columns of S a block owns (its first `cols_per_block` threads; all threads stage rows)
 };
 
 __device__ __forceinline__ float tw_logsigmoid(float x) {
@@ -50,7 +52,7 @@ __device__ __forceinline__ float tw_logsigmoid(float x) {
 }
 
 template <typename T, int MODE>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 linear_recurrence_kernel(RecArgs a) {
     extern __shared__ float sm[];
     constexpr int DK = TW_DK, C = TW_REC_CHUNK;
@@ -61,15 +63,63 @@ linear_recurrence_kernel(RecArgs a) {
     if (len <= 0) return;
     const int start = a.seq_q_start[s];
     const int Dv = a.Dv, cols = MODE == TW_REC_MLSTM ? Dv + 1 : Dv;
-    const int j = blockIdx.z * blockDim.x + threadIdx.x;
-    const bool live = j < cols;
-    float* sq = sm;                         // [C][DK]
-    float* sk = sq + C * DK;                // [C][DK]
-    float* sw = sk + C * DK;                // [C][DK] (wkv) or [C][2] gates (mlstm)
-    float* sv = sw + (MODE == TW_REC_WKV ? C * DK : (MODE == TW_REC_MLSTM ? 2 * C : 0));   // [C][columns of this block]
-    float* su = sv + C * blockDim.x;        // [DK] bonus (wkv)
+    const int per = a.cols_per_block;
+    const int j = blockIdx.z * per + threadIdx.x;
+    const bool walks = threadIdx.x < per;            // the threads that own a column; the others only stage rows
+    const bool live = walks && j < cols;
+    // a staged chunk: q [C][DK], k [C][DK], w [C][DK] (wkv) or gates [C][2] (mlstm), v [C][per]; two of them, so that
+    // the rows of the next 16 tokens are staged while the state walks through these
+    const int extra = MODE == TW_REC_WKV ? C * DK : (MODE == TW_REC_MLSTM ? 2 * C : 0);
+    const int chunk_floats = 2 * C * DK + extra + C * per;
+    float* su = sm + 2 * chunk_floats;      // [DK] bonus (wkv)
     const long long head_state = (long long)DK * cols + (MODE == TW_REC_MLSTM ? 1 : 0);
     float* slot = a.state + (size_t)a.seq_slot[s] * a.state_stride + (size_t)h * head_state;
+    const T* __restrict__ gq = (const T*)a.q;
+    const T* __restrict__ gk = (const T*)a.k;
+    const T* __restrict__ gv = (const T*)a.v;
+    const int half = a.rot_dims >> 1;
+
+    // ---- the rows of up to C tokens from t0 on, as fp32: rotation, scaling, decays and gates are evaluated here
+    auto stage = [&](int t0, float* buf, int tid, int nthreads) {
+        const int ct = min(C, len - t0);
+        float* sq = buf;
+        float* sk = sq + C * DK;
+        float* sw = sk + C * DK;
+        float* sv = sw + extra;
+#pragma unroll 4
+        for (int e = tid; e < ct * DK; e += nthreads) {
+            const int t = e / DK, i = e - t * DK;
+            const size_t row = (size_t)(start + t0 + t);
+            const T* qr = gq + row * a.q_stride + h * DK;
+            const T* kr = gk + row * a.k_stride + h * DK;
+            float qv = tw_to_float(qr[i]), kv = tw_to_float(kr[i]);
+            if (MODE == TW_REC_RETENTION && i < a.rot_dims) {
+                const int p = i < half ? i : i - half;
+                const float qo = tw_to_float(qr[i < half ? i + half : i - half]);
+                const float ko = tw_to_float(kr[i < half ? i + half : i - half]);
+                float sn, cs;
+                sincosf((float)a.positions[row] * a.inv_freq[p], &sn, &cs);
+                if (i < half) { qv = qv * cs - qo * sn; kv = kv * cs - ko * sn; }
+                else { qv = qv * cs + qo * sn; kv = kv * cs + ko * sn; }
+            }
+            sq[e] = qv * a.q_scale;
+            sk[e] = kv * a.k_scale;
+            if (MODE == TW_REC_WKV)
+                sw[e] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
+        }
+        for (int e = tid; e < ct * per; e += nthreads) {     // the block's own columns of v
+            const int t = e / per, c = blockIdx.z * per + (e - t * per);
+            if (c < Dv) sv[e] = tw_to_float(gv[(size_t)(start + t0 + t) * a.v_stride + h * Dv + c]);
+        }
+        if (MODE == TW_REC_MLSTM) {
+            for (int t = tid; t < ct; t += nthreads) {
+                const float* g = a.wpre + (size_t)(start + t0 + t) * a.wpre_stride;
+                const float pi = g[h] + a.p0[h], pf = g[a.H + h] + a.p0[a.H + h];
+                sw[2 * t] = a.cap * tanhf(pi / a.cap);
+                sw[2 * t + 1] = tw_logsigmoid(a.cap * tanhf(pf / a.cap));
+            }
+        }
+    };
 
     float S[DK];
     float m = 0.f;
@@ -82,119 +132,97 @@ linear_recurrence_kernel(RecArgs a) {
         for (int i = threadIdx.x; i < DK; i += blockDim.x) su[i] = a.p1[h * DK + i];
     }
     const float decay = MODE == TW_REC_RETENTION ? a.p0[h] : 0.f;
-    const int half = a.rot_dims >> 1;
+    const int stagers = (int)blockDim.x - per;       // threads that own no column
 
-    for (int t0 = 0; t0 < len; t0 += C) {
+    stage(0, sm, threadIdx.x, blockDim.x);
+    __syncthreads();
+    for (int t0 = 0, c = 0; t0 < len; t0 += C, ++c) {
         const int ct = min(C, len - t0);
-        __syncthreads();
-        // ---- stage the rows of ct tokens as fp32
-        for (int e = threadIdx.x; e < ct * DK; e += blockDim.x) {
-            const int t = e / DK, i = e - t * DK;
-            const size_t row = (size_t)(start + t0 + t);
-            const T* qr = (const T*)a.q + row * a.q_stride + h * DK;
-            const T* kr = (const T*)a.k + row * a.k_stride + h * DK;
-            float qv = tw_to_float(qr[i]), kv = tw_to_float(kr[i]);
-            if (MODE == TW_REC_RETENTION && i < a.rot_dims) {
-                const int p = i < half ? i : i - half;
-                float sn, cs;
-                sincosf((float)a.positions[row] * a.inv_freq[p], &sn, &cs);
-                if (i < half) {
-                    qv = qv * cs - tw_to_float(qr[i + half]) * sn;
-                    kv = kv * cs - tw_to_float(kr[i + half]) * sn;
-                } else {
-                    qv = qv * cs + tw_to_float(qr[i - half]) * sn;
-                    kv = kv * cs + tw_to_float(kr[i - half]) * sn;
+        float* buf = sm + (c & 1) * chunk_floats;
+        float* next = sm + ((c + 1) & 1) * chunk_floats;
+        const bool more = t0 + C < len;
+        if (!walks && more) stage(t0 + C, next, threadIdx.x - per, stagers);
+        if (live) {
+            const float* sq = buf;
+            const float* sk = sq + C * DK;
+            const float* sw = sk + C * DK;
+            const float* sv = sw + extra;
+            // ---- the recurrence, token by token
+            for (int t = 0; t < ct; ++t) {
+                const float* q = sq + t * DK;
+                const float* k = sk + t * DK;
+                const float vj = (MODE == TW_REC_MLSTM && j == Dv) ? 1.f : sv[t * per + threadIdx.x];
+                // four partial sums (key channels i mod 4), added at the end: the same order in every step, whatever its size
+                float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+                float fa = 0.f, fb = 0.f;
+                if (MODE == TW_REC_MLSTM) {
+                    const float li = sw[2 * t], lf = sw[2 * t + 1];
+                    const float m_new = fmaxf(lf + m, li);
+                    fa = expf(lf + m - m_new);
+                    fb = expf(li - m_new) * vj;
+                    m = m_new;
                 }
-            }
-            sq[e] = qv * a.q_scale;
-            sk[e] = kv * a.k_scale;
-            if (MODE == TW_REC_WKV)
-                sw[e] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
-        }
-        if (j < Dv) {                                    // this thread's own column of v
-            for (int t = 0; t < ct; ++t)
-                sv[t * blockDim.x + threadIdx.x] = tw_to_float(((const T*)a.v)[(size_t)(start + t0 + t) * a.v_stride + h * Dv + j]);
-        }
-        if (MODE == TW_REC_MLSTM) {
-            for (int t = threadIdx.x; t < ct; t += blockDim.x) {
-                const float* g = a.wpre + (size_t)(start + t0 + t) * a.wpre_stride;
-                const float pi = g[h] + a.p0[h], pf = g[a.H + h] + a.p0[a.H + h];
-                sw[2 * t] = a.cap * tanhf(pi / a.cap);
-                sw[2 * t + 1] = tw_logsigmoid(a.cap * tanhf(pf / a.cap));
-            }
-        }
-        __syncthreads();
-        if (!live) continue;
-        // ---- the recurrence, token by token
-        for (int t = 0; t < ct; ++t) {
-            const float* q = sq + t * DK;
-            const float* k = sk + t * DK;
-            const float vj = (MODE == TW_REC_MLSTM && j == Dv) ? 1.f : sv[t * blockDim.x + threadIdx.x];
-            // four partial sums (key channels i mod 4), added at the end: the same order in every step, whatever its size
-            float acc4[4] = {0.f, 0.f, 0.f, 0.f};
-            float fa = 0.f, fb = 0.f;
-            if (MODE == TW_REC_MLSTM) {
-                const float li = sw[2 * t], lf = sw[2 * t + 1];
-                const float m_new = fmaxf(lf + m, li);
-                fa = expf(lf + m - m_new);
-                fb = expf(li - m_new) * vj;
-                m = m_new;
-            }
-            const float* w = sw + t * DK;
-            if constexpr (DK % 4 == 0) {
-                const float4* q4 = reinterpret_cast<const float4*>(q);
-                const float4* k4 = reinterpret_cast<const float4*>(k);
-                const float4* w4 = reinterpret_cast<const float4*>(w);
-                const float4* u4 = reinterpret_cast<const float4*>(su);
+                const float* w = sw + t * DK;
+                if constexpr (DK % 4 == 0) {
+                    const float4* q4 = reinterpret_cast<const float4*>(q);
+                    const float4* k4 = reinterpret_cast<const float4*>(k);
+                    const float4* w4 = reinterpret_cast<const float4*>(w);
+                    const float4* u4 = reinterpret_cast<const float4*>(su);
 #pragma unroll
-                for (int i4 = 0; i4 < DK / 4; ++i4) {
-                    const float4 qq = q4[i4], kk = k4[i4];
-                    const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
-                    float wa[4] = {0.f, 0.f, 0.f, 0.f}, ua[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (MODE == TW_REC_WKV) {
-                        const float4 ww = w4[i4], uu = u4[i4];
-                        wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w;
-                        ua[0] = uu.x; ua[1] = uu.y; ua[2] = uu.z; ua[3] = uu.w;
+                    for (int i4 = 0; i4 < DK / 4; ++i4) {
+                        const float4 qq = q4[i4], kk = k4[i4];
+                        const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
+                        float wa[4] = {0.f, 0.f, 0.f, 0.f}, ua[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (MODE == TW_REC_WKV) {
+                            const float4 ww = w4[i4], uu = u4[i4];
+                            wa[0] = ww.x; wa[1] = ww.y; wa[2] = ww.z; wa[3] = ww.w;
+                            ua[0] = uu.x; ua[1] = uu.y; ua[2] = uu.z; ua[3] = uu.w;
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int i = 4 * i4 + e;
+                            if (MODE == TW_REC_RETENTION) {
+                                S[i] = decay * S[i] + ka[e] * vj;
+                                acc4[e] += qa[e] * S[i];
+                            } else if (MODE == TW_REC_WKV) {
+                                const float kv = ka[e] * vj;
+                                acc4[e] += qa[e] * (S[i] + ua[e] * kv);
+                                S[i] = wa[e] * S[i] + kv;
+                            } else {
+                                S[i] = fa * S[i] + fb * ka[e];
+                                acc4[e] += qa[e] * S[i];
+                            }
+                        }
                     }
+                } else {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i = 4 * i4 + e;
+                    for (int i = 0; i < DK; ++i) {
                         if (MODE == TW_REC_RETENTION) {
-                            S[i] = decay * S[i] + ka[e] * vj;
-                            acc4[e] += qa[e] * S[i];
+                            S[i] = decay * S[i] + k[i] * vj;
+                            acc4[i & 3] += q[i] * S[i];
                         } else if (MODE == TW_REC_WKV) {
-                            const float kv = ka[e] * vj;
-                            acc4[e] += qa[e] * (S[i] + ua[e] * kv);
-                            S[i] = wa[e] * S[i] + kv;
+                            const float kv = k[i] * vj;
+                            acc4[i & 3] += q[i] * (S[i] + su[i] * kv);
+                            S[i] = w[i] * S[i] + kv;
                         } else {
-                            S[i] = fa * S[i] + fb * ka[e];
-                            acc4[e] += qa[e] * S[i];
+                            S[i] = fa * S[i] + fb * k[i];
+                            acc4[i & 3] += q[i] * S[i];
                         }
                     }
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < DK; ++i) {
-                    if (MODE == TW_REC_RETENTION) {
-                        S[i] = decay * S[i] + k[i] * vj;
-                        acc4[i & 3] += q[i] * S[i];
-                    } else if (MODE == TW_REC_WKV) {
-                        const float kv = k[i] * vj;
-                        acc4[i & 3] += q[i] * (S[i] + su[i] * kv);
-                        S[i] = w[i] * S[i] + kv;
-                    } else {
-                        S[i] = fa * S[i] + fb * k[i];
-                        acc4[i & 3] += q[i] * S[i];
-                    }
-                }
+                const float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+                const size_t row = (size_t)(start + t0 + t);
+                if (MODE == TW_REC_MLSTM && j == Dv)
+                    a.den[row * a.H + h] = fmaxf(fabsf(acc), expf(-m)) + 1e-6f;
+                else
+                    a.out[row * ((size_t)a.H * Dv) + (size_t)h * Dv + j] = acc;
             }
-            const float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
-            const size_t row = (size_t)(start + t0 + t);
-            if (MODE == TW_REC_MLSTM && j == Dv)
-                a.den[row * a.H + h] = fmaxf(fabsf(acc), expf(-m)) + 1e-6f;
-            else
-                a.out[row * ((size_t)a.H * Dv) + (size_t)h * Dv + j] = acc;
         }
+        if (stagers <= 0 && more) {                  // every thread owns a column: they stage together, between the chunks
+            __syncthreads();
+            stage(t0 + C, next, threadIdx.x, blockDim.x);
+        }
+        __syncthreads();
     }
     if (!a.write_state) return;
     if (live) {
@@ -211,21 +239,26 @@ linear_recurrence_kernel(RecArgs a) {
 }
 
 template <typename T, int MODE>
-static int launch_recurrence(const RecArgs& a, int n_seqs, cudaStream_t stream) {
+static int launch_recurrence(const RecArgs& a, int n_seqs, bool long_portions, cudaStream_t stream) {
     const int cols = MODE == TW_REC_MLSTM ? a.Dv + 1 : a.Dv;
-    // columns per block: as many as still give the GPU a block per SM, at least a warp's worth
+    // columns per block: as many as still give the GPU a block per SM, at least a warp's worth.  A block has four
+    // warps at least: all of them stage the rows (loads, rotation, decays), the first `per` threads walk the state
     int per = 128;
     while (per > 32 && (long long)a.H * n_seqs * ((cols + per - 1) / per) < 148) per >>= 1;
     if (per > ((cols + 31) / 32) * 32) per = ((cols + 31) / 32) * 32;
-    size_t floats = 2 * TW_REC_CHUNK * TW_DK + (size_t)TW_REC_CHUNK * per + TW_DK;
-    floats += MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_DK : 2 * TW_REC_CHUNK;
-    const size_t smem = floats * sizeof(float);
+    RecArgs b = a;
+    b.cols_per_block = per;
+    const size_t chunk = 2 * TW_REC_CHUNK * TW_DK + (size_t)TW_REC_CHUNK * per
+                         + (MODE == TW_REC_WKV ? TW_REC_CHUNK * TW_DK : (MODE == TW_REC_MLSTM ? 2 * TW_REC_CHUNK : 0));
+    const size_t smem = (2 * chunk + TW_DK) * sizeof(float);
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(linear_recurrence_kernel<T, MODE>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return tw_launch(linear_recurrence_kernel<T, MODE>, dim3(a.H, n_seqs, (cols + per - 1) / per), dim3(per), smem, stream, 1, a);
+    // steps of single tokens stage one chunk and walk it: a thread per column; longer portions get warps that only stage
+    const int threads = long_portions ? 256 : per;
+    return tw_launch(linear_recurrence_kernel<T, MODE>, dim3(a.H, n_seqs, (cols + per - 1) / per), dim3(threads), smem, stream, 1, b);
 }
 
 TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void* q, int q_stride, const void* k, int k_stride,
@@ -234,8 +267,9 @@ TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void*
                                    float cap, float* state, long long state_stride, const void* tail_src, int tail_stride,
                                    int tail_width, long long tail_offset, const int* positions, const int* seq_slot,
                                    const int* seq_q_start, const int* seq_q_len, int n_seqs, int H, int Dk, int Dv,
-                                   int write_state, int dtype, cudaStream_t stream) {
+                                   int write_state, int max_q_len, int dtype, cudaStream_t stream) {
     if (n_seqs <= 0 || H <= 0) return 0;
+    const bool lp = max_q_len > TW_REC_CHUNK;
     if (Dk != TW_DK || Dv <= 0 || Dv > 256 || rot_dims < 0 || rot_dims > Dk || (rot_dims & 1)) return (int)cudaErrorInvalidValue;
     RecArgs a;
     a.out = out; a.den = den; a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
@@ -243,19 +277,19 @@ TW_EXPORT int tw_linear_recurrence(int mode, float* out, float* den, const void*
     a.k_scale = k_scale; a.q_scale = q_scale; a.cap = cap; a.state = state; a.state_stride = state_stride;
     a.tail_src = tail_src; a.tail_stride = tail_stride; a.tail_width = tail_width; a.tail_offset = tail_offset;
     a.positions = positions; a.seq_slot = seq_slot; a.seq_q_start = seq_q_start; a.seq_q_len = seq_q_len;
-    a.H = H; a.Dv = Dv; a.write_state = write_state;
+    a.H = H; a.Dv = Dv; a.write_state = write_state; a.cols_per_block = 0;
     const bool f32 = dtype == TW_F32;
     switch (mode) {
     case TW_REC_RETENTION:
-        return f32 ? launch_recurrence<float, TW_REC_RETENTION>(a, n_seqs, stream)
-                   : launch_recurrence<__nv_bfloat16, TW_REC_RETENTION>(a, n_seqs, stream);
+        return f32 ? launch_recurrence<float, TW_REC_RETENTION>(a, n_seqs, lp, stream)
+                   : launch_recurrence<__nv_bfloat16, TW_REC_RETENTION>(a, n_seqs, lp, stream);
     case TW_REC_WKV:
         if (Dv != Dk) return (int)cudaErrorInvalidValue;
-        return f32 ? launch_recurrence<float, TW_REC_WKV>(a, n_seqs, stream)
-                   : launch_recurrence<__nv_bfloat16, TW_REC_WKV>(a, n_seqs, stream);
+        return f32 ? launch_recurrence<float, TW_REC_WKV>(a, n_seqs, lp, stream)
+                   : launch_recurrence<__nv_bfloat16, TW_REC_WKV>(a, n_seqs, lp, stream);
     case TW_REC_MLSTM:
-        return f32 ? launch_recurrence<float, TW_REC_MLSTM>(a, n_seqs, stream)
-                   : launch_recurrence<__nv_bfloat16, TW_REC_MLSTM>(a, n_seqs, stream);
+        return f32 ? launch_recurrence<float, TW_REC_MLSTM>(a, n_seqs, lp, stream)
+                   : launch_recurrence<__nv_bfloat16, TW_REC_MLSTM>(a, n_seqs, lp, stream);
     }
     return (int)cudaErrorInvalidValue;
 }

@@ -19,19 +19,53 @@ __device__ __forceinline__ float tw_dot_row(const T* __restrict__ w, const float
     return tw_warp_sum(acc);
 }
 
-// bf16 rows whose length is a multiple of 8 and whose start is 16-byte aligned: eight values per load
-__device__ __forceinline__ float tw_dot_row8(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
-    float acc = 0.f;
-    for (int i = lane * 8; i < n; i += 256) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
-        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+// bf16 rows whose length is a multiple of 8 and whose start is 16-byte aligned: eight values per load, four
+// loads of a lane under way at a time (a row is streamed once; what bounds it is how much is in flight)
+__device__ __forceinline__ float tw_fma8(uint4 raw, const float* __restrict__ x, float acc) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(p[e]);
-            acc += f.x * x[i + 2 * e] + f.y * x[i + 2 * e + 1];
-        }
+    for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p[e]);
+        acc += f.x * x[2 * e] + f.y * x[2 * e + 1];
     }
-    return tw_warp_sum(acc);
+    return acc;
+}
+
+__device__ __forceinline__ uint4 tw_stream16(const __nv_bfloat16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float tw_dot_row8(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int i = lane * 8;
+    for (; i + 768 < n; i += 1024) {
+        const uint4 r0 = tw_stream16(w + i), r1 = tw_stream16(w + i + 256), r2 = tw_stream16(w + i + 512), r3 = tw_stream16(w + i + 768);
+        a0 = tw_fma8(r0, x + i, a0); a1 = tw_fma8(r1, x + i + 256, a1);
+        a2 = tw_fma8(r2, x + i + 512, a2); a3 = tw_fma8(r3, x + i + 768, a3);
+    }
+    for (; i < n; i += 256) a0 = tw_fma8(tw_stream16(w + i), x + i, a0);
+    return tw_warp_sum((a0 + a1) + (a2 + a3));
+}
+
+// two rows of equal length at once (an expert's gate row and its up row): eight loads of a lane under way
+__device__ __forceinline__ void tw_dot2_row8(const __nv_bfloat16* __restrict__ wa, const __nv_bfloat16* __restrict__ wb,
+                                             const float* __restrict__ x, int n, int lane, float& da, float& db) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+    int i = lane * 8;
+    for (; i + 768 < n; i += 1024) {
+        const uint4 r0 = tw_stream16(wa + i), r1 = tw_stream16(wa + i + 256), r2 = tw_stream16(wa + i + 512), r3 = tw_stream16(wa + i + 768);
+        const uint4 s0 = tw_stream16(wb + i), s1 = tw_stream16(wb + i + 256), s2 = tw_stream16(wb + i + 512), s3 = tw_stream16(wb + i + 768);
+        a0 = tw_fma8(r0, x + i, a0); a1 = tw_fma8(r1, x + i + 256, a1); a2 = tw_fma8(r2, x + i + 512, a2); a3 = tw_fma8(r3, x + i + 768, a3);
+        b0 = tw_fma8(s0, x + i, b0); b1 = tw_fma8(s1, x + i + 256, b1); b2 = tw_fma8(s2, x + i + 512, b2); b3 = tw_fma8(s3, x + i + 768, b3);
+    }
+    for (; i < n; i += 256) {
+        a0 = tw_fma8(tw_stream16(wa + i), x + i, a0);
+        b0 = tw_fma8(tw_stream16(wb + i), x + i, b0);
+    }
+    da = tw_warp_sum((a0 + a1) + (a2 + a3));
+    db = tw_warp_sum((b0 + b1) + (b2 + b3));
 }
 
 template <typename T> __device__ __forceinline__ float tw_dot(const T* w, const float* x, int n, int lane, bool vec);
@@ -40,6 +74,20 @@ template <> __device__ __forceinline__ float tw_dot<float>(const float* w, const
 }
 template <> __device__ __forceinline__ float tw_dot<__nv_bfloat16>(const __nv_bfloat16* w, const float* x, int n, int lane, bool vec) {
     return vec ? tw_dot_row8(w, x, n, lane) : tw_dot_row(w, x, n, lane);
+}
+
+template <typename T> __device__ __forceinline__ void tw_dot2(const T* wa, const T* wb, const float* x, int n, int lane, bool vec,
+                                                              float& da, float& db);
+template <> __device__ __forceinline__ void tw_dot2<float>(const float* wa, const float* wb, const float* x, int n, int lane, bool,
+                                                           float& da, float& db) {
+    da = tw_dot_row(wa, x, n, lane);
+    db = tw_dot_row(wb, x, n, lane);
+}
+template <> __device__ __forceinline__ void tw_dot2<__nv_bfloat16>(const __nv_bfloat16* wa, const __nv_bfloat16* wb, const float* x,
+                                                                   int n, int lane, bool vec, float& da, float& db) {
+    if (vec) { tw_dot2_row8(wa, wb, x, n, lane, da, db); return; }
+    da = tw_dot_row(wa, x, n, lane);
+    db = tw_dot_row(wb, x, n, lane);
 }
 
 template <typename T>
@@ -119,8 +167,8 @@ moe_gate_up_kernel(T* __restrict__ act, const T* __restrict__ h, int h_stride, c
     const T* wu = wg + (size_t)F * width;
     const int f0 = blockIdx.y * rows_per_block, f1 = min(F, f0 + rows_per_block);
     for (int f = f0 + warp; f < f1; f += TW_MOE_WARPS) {
-        const float g = tw_dot<T>(wg + (size_t)f * width, sm, width, lane, vec);
-        const float u = tw_dot<T>(wu + (size_t)f * width, sm, width, lane, vec);
+        float g, u;
+        tw_dot2<T>(wg + (size_t)f * width, wu + (size_t)f * width, sm, width, lane, vec, g, u);
         if (lane == 0) act[(size_t)pair * F + f] = tw_from_float<T>(g / (1.0f + expf(-g)) * u);
     }
 }

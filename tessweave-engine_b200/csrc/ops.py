@@ -1217,13 +1217,14 @@ def linear_recurrence(mode: int, out: torch.Tensor, den: torch.Tensor | None, q:
                       seq_q_len: torch.Tensor, n_seqs: int, heads: int, key_dim: int, value_dim: int, write_state: bool = True,
                       pre: torch.Tensor | None = None, p0: torch.Tensor | None = None, p1: torch.Tensor | None = None,
                       inv_freq: torch.Tensor | None = None, rot_dims: int = 0, q_scale: float = 1.0, k_scale: float = 1.0,
-                      cap: float = 1.0, tail: torch.Tensor | None = None, tail_offset: int = 0) -> None:
+                      cap: float = 1.0, tail: torch.Tensor | None = None, tail_offset: int = 0, max_q_len: int = 1 << 30) -> None:
     """Walk every request's rows of the step through its matrix state (csrc/linear_recurrence.cu): ``out`` fp32
     [rows, heads * value_dim] receives the raw outputs, ``den`` fp32 [rows, heads] the mLSTM denominators.  q, k, v are
     column slices of the projected rows (heads side by side).  ``pre``: fp32 rows the rule needs beside them (wkv:
     the projected decay [rows, heads * key_dim]; mlstm: the gates' pre-activations [rows, 2 * heads]); ``p0`` / ``p1``
     fp32 constants (wkv: decay offset and bonus; retention: decay per head; mlstm: gate biases).  ``tail``: rows whose
-    last one per request is copied into the state behind the heads (wkv's token shift), at ``tail_offset``."""
+    last one per request is copied into the state behind the heads (wkv's token shift), at ``tail_offset``.
+    ``max_q_len``: the longest portion of the step (a hint: steps of single tokens launch smaller blocks)."""
     _cuda(out, den, q, k, v, state, positions, seq_slot, seq_q_start, seq_q_len, pre, p0, p1, inv_freq, tail)
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == heads * value_dim, "recurrence: out must be fp32 [rows, H * Dv]")
     _need(q.dtype == k.dtype == v.dtype and q.stride(1) == k.stride(1) == v.stride(1) == 1, "recurrence: q, k, v of one type, unit column stride")
@@ -1240,7 +1241,7 @@ def linear_recurrence(mode: int, out: torch.Tensor, den: torch.Tensor | None, q:
         c_float(q_scale), c_float(k_scale), c_float(cap), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(tail),
         c_int(0 if tail is None else tail.stride(0)), c_int(0 if tail is None else tail.shape[1]), ctypes.c_longlong(tail_offset),
         _ptr(positions), _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(heads), c_int(key_dim),
-        c_int(value_dim), c_int(1 if write_state else 0), c_int(dtype_code(q.dtype)), _stream())
+        c_int(value_dim), c_int(1 if write_state else 0), c_int(max_q_len), c_int(dtype_code(q.dtype)), _stream())
     _check(code, "linear_recurrence")
 
 

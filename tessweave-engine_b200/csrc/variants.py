@@ -14,6 +14,7 @@ _SPECIALISED: dict[str, list[dict]] = {
     "attention_decode_tma": [{"TW_HEAD_DIM": d} for d in (64, 128)],
     "sigmoid_attention_bf16": [{"TW_HEAD_DIM": d} for d in (64, 128)],
     "sigmoid_attention_tcgen05": [{"TW_HEAD_DIM": d, "TW_SIG_KEY_TILE": 128} for d in (64, 128)],
+    "linear_recurrence": [{"TW_DK": d} for d in (32, 64, 128)],       # the key size of a head: a column of the state in registers
 }
 
 

@@ -294,7 +294,7 @@ def sapatar_kernel_table(config: dict, batch: int, context: int, prefill_tokens:
             nbytes = m * H * (2 * Dk + Dv) * 2 + m * H * Dv * 4 + 2 * requests * numel * 4 + (m * H * Dk * 4 if rule == ops.RECURRENCE_WKV else 0)
             add(f"{phase}: {name} recurrence, {H} heads of {Dk} x {Dv}", m,
                 [(lambda s=s: ops.linear_recurrence(rule, s[4], s[5] if rule == ops.RECURRENCE_MLSTM else None, s[0], s[1], s[2], s[3],
-                                                    positions, slots, starts, lens, requests, H, Dk, Dv, True, **extra)) for s in sets],
+                                                    positions, slots, starts, lens, requests, H, Dk, Dv, True, max_q_len=per, **extra)) for s in sets],
                 nbytes, 0.0, reps=2 if phase == "prefill" else 8,
                 note=f"{4.0 * m * H * Dk * Dv / 1e9:.2f} GFLOP of fp32 multiply-adds outside the tensor cores")
             del sets

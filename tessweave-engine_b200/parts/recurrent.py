@@ -100,7 +100,8 @@ class MatrixStateMixer(Mixer):
         raw = ws.get("recurrence.raw", (n, self.v_size), torch.float32)
         den = ws.get("recurrence.den", (n, self.n_heads), torch.float32) if self.rule == ops.RECURRENCE_MLSTM else None
         ops.linear_recurrence(self.rule, raw, den, q, k, v, cache.state, ctx.positions, ctx.seq_slot, ctx.seq_q_start,
-                              ctx.seq_q_len, ctx.n_seqs, self.n_heads, self.key_dim, self.value_dim, write_state, **rule_args)
+                              ctx.seq_q_len, ctx.n_seqs, self.n_heads, self.key_dim, self.value_dim, write_state,
+                              max_q_len=ctx.max_q_len, **rule_args)
         return raw, den
 
     def _finish(self, ctx: StepContext, raw, den, weight, gate):
