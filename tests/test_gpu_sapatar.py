@@ -385,13 +385,31 @@ def float32_noise(folders, plain_rows):
     return out
 
 
+@pytest.fixture(scope="module")
+def bfloat16_noise(folders, plain_rows):
+    """What perturbations of bfloat16's size do to each row by themselves: the plain implementation (float64) with
+    every matrix element moved by a relative 2^-8 times a normal draw, against itself.  Rows behind a nearly
+    orthogonal query and key at a request's first tokens, or near a denominator's floor, move by tens of per cent."""
+    out = {}
+    for name in SAPATAR_CONFIGS:
+        config, weights = plain.read_folder(folders[name, "bfloat16"], torch.float64)
+        g = torch.Generator().manual_seed(99)
+        moved = {k: v * (1 + 2.0 ** -8 * torch.randn(v.shape, generator=g, dtype=torch.float64)) if v.dim() == 2 else v
+                 for k, v in weights.items()}
+        for rid, t in requests_for(name).items():
+            low = plain.forward(config, moved, t).float().numpy()
+            out[name, rid] = [row_error(low[p], plain_rows[name, "bfloat16"][rid][p]) for p in range(len(t))]
+    return out
+
+
 def compare(rows, want, dtype, what, noise=None):
     """Every logits row against the plain one (float64).  float32: every row within 5e-5 of its spread plus four
     times what the plain implementation loses at that row when it runs in float32 itself.  bfloat16: the design has
     places where rounding alone moves a row far (under the matrix memory's normaliser the sign of a nearly orthogonal
     query and key decides a head's output at a request's first tokens), so the rows are judged together: the median
-    within 6 % (observed: 1 to 4.4 %), at most five rows in a hundred beyond 8 % plus 20,000 times the float32 loss,
-    none that is not finite.  A lost state, a key outside its window or a wrong page moves rows by their whole size."""
+    within 6 % (observed: 1 to 4.4 %), at most five rows in a hundred beyond 8 % plus three times what a perturbation
+    of bfloat16's size does to that row of the plain implementation (``noise``), none that is not finite.  A lost
+    state, a key outside its window or a wrong page moves rows by their whole size."""
     errors, over = [], []
     for (rid, p), row in rows.items():
         err = row_error(row, want[rid][p])
@@ -399,7 +417,7 @@ def compare(rows, want, dtype, what, noise=None):
         lost = noise[rid][p] if noise else 0.0
         if dtype == "float32":
             assert err <= 5e-5 + 4 * lost, f"{what}: {rid}[{p}] differs by {err:.3g} of the row's spread (float32 alone: {lost:.3g})"
-        elif err > 8e-2 + 2e4 * lost:
+        elif err > 8e-2 + 3 * lost:
             over.append((rid, p, round(err, 3)))
         errors.append(err)
     if dtype == "bfloat16":
@@ -418,7 +436,7 @@ SCHEDULES = {
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
-def test_every_cutting_gives_the_plain_logits(name, dtype, folders, plain_rows, float32_noise, tmp_path):
+def test_every_cutting_gives_the_plain_logits(name, dtype, folders, plain_rows, float32_noise, bfloat16_noise, tmp_path):
     """Whole prompts; most of a prompt and its last 32 tokens one by one; portions down to two tokens; token by
     token from the first; four live requests in mixed batches with so few pages and slots that both are used
     again (freed pages are filled with NaN first)."""
@@ -428,7 +446,8 @@ def test_every_cutting_gives_the_plain_logits(name, dtype, folders, plain_rows, 
         rows = replay_in_process(folders[name, dtype], dtype, steps, tmp_path / kind, block_size=SAPATAR_PAGE[name],
                                  max_tokens=max_live_tokens(steps))
         assert rows, kind
-        compare(rows, plain_rows[name, dtype], dtype, f"{name} {kind}", {rid: float32_noise[name, rid] for rid in reqs})
+        noise = float32_noise if dtype == "float32" else bfloat16_noise
+        compare(rows, plain_rows[name, dtype], dtype, f"{name} {kind}", {rid: noise[name, rid] for rid in reqs})
 
 
 def test_batches_and_cuts_do_not_change_a_request(folders, tmp_path):
