@@ -11,8 +11,9 @@
 //                      i = cap tanh((pi + bi) / cap), f = logsigmoid(cap tanh((pf + bf) / cap)); m is 0 before
 //                      the first token.  n is carried as one more column of S (a value that is always 1).
 //
-// One block per (head, request, slice of the columns of S): thread j owns one column of S in registers (TW_DK
-// values, a compile-time size) and walks the request's rows of this step in order (the columns of a head are
+// One block per (head, request, slice of the columns of S): a thread owns a column of S in registers (TW_DK
+// values, a compile-time size; where that size is a multiple of 16 four lanes share a column, a quarter of its key
+// channels each) and walks the request's rows of this step in order (the columns of a head are
 // independent of one another, so a head is spread over as many blocks as it takes to fill the GPU; in steps with
 // long portions the block's other warps stage the next 16 tokens meanwhile); the rows of 16 tokens at a time are staged in
 // shared memory as fp32 (rotation, scaling, decays and gates are evaluated there, once per value).  The
@@ -25,6 +26,9 @@
 #define TW_DK 64
 #endif
 #define TW_REC_CHUNK 16
+// Threads that share a column of the state: each owns TW_DK / TW_REC_KSPLIT of its key channels (lanes l, l + 8,
+// l + 16, l + 24 of a warp), and their partial outputs are added by two shuffles.
+#define TW_REC_KSPLIT ((TW_DK % 16 == 0) ? 4 : 1)
 
 enum : int { TW_REC_RETENTION = 0, TW_REC_WKV = 1, TW_REC_MLSTM = 2 };
 
@@ -52,10 +56,10 @@ __device__ __forceinline__ float tw_logsigmoid(float x) {
 }
 
 template <typename T, int MODE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 linear_recurrence_kernel(RecArgs a) {
     extern __shared__ float sm[];
-    constexpr int DK = TW_DK, C = TW_REC_CHUNK;
+    constexpr int DK = TW_DK, C = TW_REC_CHUNK, KS = TW_REC_KSPLIT, SK = DK / KS;
     tw_grid_wait();
     tw_grid_launch_dependents();
     const int h = blockIdx.x, s = blockIdx.y;
@@ -64,8 +68,12 @@ linear_recurrence_kernel(RecArgs a) {
     const int start = a.seq_q_start[s];
     const int Dv = a.Dv, cols = MODE == TW_REC_MLSTM ? Dv + 1 : Dv;
     const int per = a.cols_per_block;
-    const int j = blockIdx.z * per + threadIdx.x;
-    const bool walks = threadIdx.x < per;            // the threads that own a column; the others only stage rows
+    // the block's first per * KS threads walk the state: with KS = 4 a warp serves 8 columns (lane & 7) and a lane the
+    // key channels [ks * SK, (ks + 1) * SK) with ks = lane >> 3; with KS = 1 a thread serves a whole column
+    const int jl = KS == 1 ? (int)threadIdx.x : (int)(threadIdx.x >> 5) * 8 + (int)(threadIdx.x & 7);
+    const int ks = KS == 1 ? 0 : (int)(threadIdx.x & 31) >> 3;
+    const int j = blockIdx.z * per + jl;
+    const bool walks = (int)threadIdx.x < per * KS;  // the threads that own (a share of) a column; the others only stage rows
     const bool live = walks && j < cols;
     // a staged chunk: q [C][DK], k [C][DK], w [C][DK] (wkv) or gates [C][2] (mlstm), v [C][per]; two of them, so that
     // the rows of the next 16 tokens are staged while the state walks through these
@@ -86,26 +94,33 @@ linear_recurrence_kernel(RecArgs a) {
         float* sk = sq + C * DK;
         float* sw = sk + C * DK;
         float* sv = sw + extra;
-#pragma unroll 4
-        for (int e = tid; e < ct * DK; e += nthreads) {
-            const int t = e / DK, i = e - t * DK;
-            const size_t row = (size_t)(start + t0 + t);
-            const T* qr = gq + row * a.q_stride + h * DK;
-            const T* kr = gk + row * a.k_stride + h * DK;
-            float qv = tw_to_float(qr[i]), kv = tw_to_float(kr[i]);
-            if (MODE == TW_REC_RETENTION && i < a.rot_dims) {
-                const int p = i < half ? i : i - half;
-                const float qo = tw_to_float(qr[i < half ? i + half : i - half]);
-                const float ko = tw_to_float(kr[i < half ? i + half : i - half]);
+        if (MODE == TW_REC_RETENTION) {
+            // a rotated pair (i, i + half) at a time: one angle, four loads, four values
+            for (int e = tid; e < ct * half; e += nthreads) {
+                const int t = e / half, i = e - t * half;
+                const size_t row = (size_t)(start + t0 + t);
+                const T* qr = gq + row * a.q_stride + h * DK;
+                const T* kr = gk + row * a.k_stride + h * DK;
+                const float q1 = tw_to_float(qr[i]), q2 = tw_to_float(qr[i + half]);
+                const float k1 = tw_to_float(kr[i]), k2 = tw_to_float(kr[i + half]);
                 float sn, cs;
-                sincosf((float)a.positions[row] * a.inv_freq[p], &sn, &cs);
-                if (i < half) { qv = qv * cs - qo * sn; kv = kv * cs - ko * sn; }
-                else { qv = qv * cs + qo * sn; kv = kv * cs + ko * sn; }
+                sincosf((float)a.positions[row] * a.inv_freq[i], &sn, &cs);
+                sq[t * DK + i] = (q1 * cs - q2 * sn) * a.q_scale;
+                sq[t * DK + i + half] = (q2 * cs + q1 * sn) * a.q_scale;
+                sk[t * DK + i] = (k1 * cs - k2 * sn) * a.k_scale;
+                sk[t * DK + i + half] = (k2 * cs + k1 * sn) * a.k_scale;
             }
-            sq[e] = qv * a.q_scale;
-            sk[e] = kv * a.k_scale;
+        }
+        const int first = MODE == TW_REC_RETENTION ? a.rot_dims : 0;     // channels from here on are not rotated
+        const int plain = DK - first;
+#pragma unroll 4
+        for (int e = tid; e < ct * plain; e += nthreads) {
+            const int t = e / plain, i = first + (e - t * plain);
+            const size_t row = (size_t)(start + t0 + t);
+            sq[t * DK + i] = tw_to_float(gq[row * a.q_stride + h * DK + i]) * a.q_scale;
+            sk[t * DK + i] = tw_to_float(gk[row * a.k_stride + h * DK + i]) * a.k_scale;
             if (MODE == TW_REC_WKV)
-                sw[e] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
+                sw[t * DK + i] = expf(-expf(a.wpre[row * a.wpre_stride + h * DK + i] + a.p0[h * DK + i]));
         }
         for (int e = tid; e < ct * per; e += nthreads) {     // the block's own columns of v
             const int t = e / per, c = blockIdx.z * per + (e - t * per);
@@ -121,18 +136,18 @@ linear_recurrence_kernel(RecArgs a) {
         }
     };
 
-    float S[DK];
+    float S[SK];
     float m = 0.f;
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DK; ++i) S[i] = slot[(size_t)i * cols + j];
+        for (int i = 0; i < SK; ++i) S[i] = slot[(size_t)(ks * SK + i) * cols + j];
     }
     if (MODE == TW_REC_MLSTM) m = slot[(size_t)DK * cols];
     if (MODE == TW_REC_WKV) {
         for (int i = threadIdx.x; i < DK; i += blockDim.x) su[i] = a.p1[h * DK + i];
     }
     const float decay = MODE == TW_REC_RETENTION ? a.p0[h] : 0.f;
-    const int stagers = (int)blockDim.x - per;       // threads that own no column
+    const int stagers = (int)blockDim.x - per * KS;  // threads that own no column
 
     stage(0, sm, threadIdx.x, blockDim.x);
     __syncthreads();
@@ -141,17 +156,17 @@ linear_recurrence_kernel(RecArgs a) {
         float* buf = sm + (c & 1) * chunk_floats;
         float* next = sm + ((c + 1) & 1) * chunk_floats;
         const bool more = t0 + C < len;
-        if (!walks && more) stage(t0 + C, next, threadIdx.x - per, stagers);
-        if (live) {
+        if (!walks && more) stage(t0 + C, next, threadIdx.x - per * KS, stagers);
+        if (walks) {                                 // (threads of a live warp whose column lies beyond the last take part in its shuffles)
             const float* sq = buf;
             const float* sk = sq + C * DK;
             const float* sw = sk + C * DK;
             const float* sv = sw + extra;
             // ---- the recurrence, token by token
             for (int t = 0; t < ct; ++t) {
-                const float* q = sq + t * DK;
-                const float* k = sk + t * DK;
-                const float vj = (MODE == TW_REC_MLSTM && j == Dv) ? 1.f : sv[t * per + threadIdx.x];
+                const float* q = sq + t * DK + ks * SK;
+                const float* k = sk + t * DK + ks * SK;
+                const float vj = (MODE == TW_REC_MLSTM && j == Dv) ? 1.f : (j < Dv ? sv[t * per + jl] : 0.f);
                 // four partial sums (key channels i mod 4), added at the end: the same order in every step, whatever its size
                 float acc4[4] = {0.f, 0.f, 0.f, 0.f};
                 float fa = 0.f, fb = 0.f;
@@ -162,14 +177,15 @@ linear_recurrence_kernel(RecArgs a) {
                     fb = expf(li - m_new) * vj;
                     m = m_new;
                 }
-                const float* w = sw + t * DK;
-                if constexpr (DK % 4 == 0) {
+                const float* w = sw + t * DK + ks * SK;
+                const float* u = su + ks * SK;
+                if constexpr (SK % 4 == 0) {
                     const float4* q4 = reinterpret_cast<const float4*>(q);
                     const float4* k4 = reinterpret_cast<const float4*>(k);
                     const float4* w4 = reinterpret_cast<const float4*>(w);
-                    const float4* u4 = reinterpret_cast<const float4*>(su);
+                    const float4* u4 = reinterpret_cast<const float4*>(u);
 #pragma unroll
-                    for (int i4 = 0; i4 < DK / 4; ++i4) {
+                    for (int i4 = 0; i4 < SK / 4; ++i4) {
                         const float4 qq = q4[i4], kk = k4[i4];
                         const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
                         float wa[4] = {0.f, 0.f, 0.f, 0.f}, ua[4] = {0.f, 0.f, 0.f, 0.f};
@@ -196,13 +212,13 @@ linear_recurrence_kernel(RecArgs a) {
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < DK; ++i) {
+                    for (int i = 0; i < SK; ++i) {
                         if (MODE == TW_REC_RETENTION) {
                             S[i] = decay * S[i] + k[i] * vj;
                             acc4[i & 3] += q[i] * S[i];
                         } else if (MODE == TW_REC_WKV) {
                             const float kv = k[i] * vj;
-                            acc4[i & 3] += q[i] * (S[i] + su[i] * kv);
+                            acc4[i & 3] += q[i] * (S[i] + u[i] * kv);
                             S[i] = w[i] * S[i] + kv;
                         } else {
                             S[i] = fa * S[i] + fb * k[i];
@@ -210,12 +226,18 @@ linear_recurrence_kernel(RecArgs a) {
                         }
                     }
                 }
-                const float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+                float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
+                if (KS > 1) {                        // the shares of a column, always added in this order
+                    acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+                    acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+                }
                 const size_t row = (size_t)(start + t0 + t);
-                if (MODE == TW_REC_MLSTM && j == Dv)
-                    a.den[row * a.H + h] = fmaxf(fabsf(acc), expf(-m)) + 1e-6f;
-                else
-                    a.out[row * ((size_t)a.H * Dv) + (size_t)h * Dv + j] = acc;
+                if (live && ks == 0) {
+                    if (MODE == TW_REC_MLSTM && j == Dv)
+                        a.den[row * a.H + h] = fmaxf(fabsf(acc), expf(-m)) + 1e-6f;
+                    else
+                        a.out[row * ((size_t)a.H * Dv) + (size_t)h * Dv + j] = acc;
+                }
             }
         }
         if (stagers <= 0 && more) {                  // every thread owns a column: they stage together, between the chunks
@@ -227,9 +249,9 @@ linear_recurrence_kernel(RecArgs a) {
     if (!a.write_state) return;
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DK; ++i) slot[(size_t)i * cols + j] = S[i];
+        for (int i = 0; i < SK; ++i) slot[(size_t)(ks * SK + i) * cols + j] = S[i];
     }
-    if (MODE == TW_REC_MLSTM && j == 0) slot[(size_t)DK * cols] = m;
+    if (MODE == TW_REC_MLSTM && live && j == 0 && ks == 0) slot[(size_t)DK * cols] = m;
     if (MODE == TW_REC_WKV && h == 0 && blockIdx.z == 0 && a.tail_src) {
         // what the next step's first token mixes with: the last row this mixer read
         const T* src = (const T*)a.tail_src + (size_t)(start + len - 1) * a.tail_stride;
@@ -243,7 +265,8 @@ static int launch_recurrence(const RecArgs& a, int n_seqs, bool long_portions, c
     const int cols = MODE == TW_REC_MLSTM ? a.Dv + 1 : a.Dv;
     // columns per block: as many as still give the GPU a block per SM, at least a warp's worth.  A block has four
     // warps at least: all of them stage the rows (loads, rotation, decays), the first `per` threads walk the state
-    int per = 128;
+    constexpr int KS = TW_REC_KSPLIT;
+    int per = KS == 1 ? 128 : 64;
     while (per > 32 && (long long)a.H * n_seqs * ((cols + per - 1) / per) < 148) per >>= 1;
     if (per > ((cols + 31) / 32) * 32) per = ((cols + 31) / 32) * 32;
     RecArgs b = a;
@@ -257,7 +280,7 @@ static int launch_recurrence(const RecArgs& a, int n_seqs, bool long_portions, c
         if (e != cudaSuccess) return (int)e;
     }
     // steps of single tokens stage one chunk and walk it: a thread per column; longer portions get warps that only stage
-    const int threads = long_portions ? 256 : per;
+    const int threads = long_portions ? per * KS + 256 : per * KS;
     return tw_launch(linear_recurrence_kernel<T, MODE>, dim3(a.H, n_seqs, (cols + per - 1) / per), dim3(threads), smem, stream, 1, b);
 }
 
