@@ -40,7 +40,7 @@ def step_ctx(rt, plan, at):
 # mechanisms alone
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("head_dim,dims,theta", [(16, 8, 1e3), (24, 24, 5e4), (64, 2, 1e6), (32, 0, 1e4), (48, 48, 2e4)])
+@pytest.mark.parametrize("head_dim,dims,theta", [(16, 8, 1e3), (24, 24, 5e4), (64, 2, 3e6), (32, 0, 1e4), (40, 40, 3e4)])
 def test_rotation_of_halves_over_part_of_a_head(dtype, head_dim, dims, theta):
     """Value i turns with value i + dims/2; the rest of a head and the heads behind stay."""
     rt = Runtime(torch.device("cuda"), dtype)
@@ -61,7 +61,7 @@ def test_rotation_of_halves_over_part_of_a_head(dtype, head_dim, dims, theta):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("copies,width", [(1, 40), (2, 36), (4, 192), (8, 1000)])
+@pytest.mark.parametrize("copies,width", [(1, 40), (2, 36), (4, 200), (8, 1000), (11, 72)])
 def test_hyper_connection_pass(dtype, copies, width):
     """Start from a row, write a sub-layer's output, read the next sub-layer's input, sum the copies: each alone
     and all in one call."""
@@ -88,14 +88,20 @@ def test_hyper_connection_pass(dtype, copies, width):
     close(total.cpu(), ref.sum(0), torch.float32, "sum", f32=3e-6)
 
 
-def run_state_mixer(rt, mixer, hidden, plain_fn, lengths=(223, 9), plan=((7, 0), (1, 4), (2, 1), (0, 1), (150, 3), (63, 0))):
+def run_state_mixer(rt, mixer, hidden, plain_fn, lengths=(223, 9), plan=((7, 0), (1, 4), (2, 1), (0, 1), (150, 3), (63, 0)),
+                    loud_row=None):
     """A mixer with a fixed-size state, cut into steps (down to one row, up to 150), two requests side by side in
-    slots 2 and 0; against the plain mixer on each whole sequence."""
+    slots 2 and 0; against the plain mixer on each whole sequence.  ``loud_row``: that row of request a is twelve
+    times as large as the others, so that what it leaves in the state outweighs everything else for as long as the
+    decays allow."""
     dtype = rt.dtype
     state = torch.zeros(3, mixer.cache_need().numel, device="cuda")
     view = StateView(state)
     g = torch.Generator().manual_seed(3)
-    ha, hb = (torch.randn(n, hidden, generator=g).to(dtype) for n in lengths)
+    ha, hb = (torch.randn(n, hidden, generator=g) for n in lengths)
+    if loud_row is not None:
+        ha[loud_row] *= 12.0
+    ha, hb = ha.to(dtype), hb.to(dtype)
     want_a, want_b = plain_fn(ha.double(), torch.arange(lengths[0])).float(), plain_fn(hb.double(), torch.arange(lengths[1])).float()
     got_a, got_b = [], []
     at = {2: 0, 0: 0}
@@ -124,7 +130,7 @@ def test_retention_alone(dtype, hidden, heads, dk, dv, rot):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden,heads,d,rank", [(48, 2, 16, 8), (40, 5, 8, 4), (36, 3, 12, 5), (128, 2, 64, 16)])
+@pytest.mark.parametrize("hidden,heads,d,rank", [(48, 2, 16, 8), (40, 5, 8, 4), (36, 3, 12, 5), (128, 2, 64, 24)])
 def test_wkv_alone(dtype, hidden, heads, d, rank):
     """Token shift across the cuts (the row before a step's first row comes from the state), decays per channel,
     the bonus for the token itself."""
@@ -156,8 +162,43 @@ def test_mlstm_alone(dtype, hidden, heads, dk, dv, cap):
     run_state_mixer(rt, mixer, hidden, lambda h, pos: plain.mixer_mlstm(h, w, "p", m, 1e-5))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kind", ["retention", "wkv", "mlstm"])
+@pytest.mark.parametrize("loud_row", [0, 3, 149])
+def test_one_token_far_back_outweighs_the_rest(dtype, kind, loud_row):
+    """Decays close to 1 and one loud token: hundreds of tokens later the outputs still consist mostly of what that
+    token left in the state (the plain outputs with and without it differ by their whole size), through cuts into
+    steps of 1 to 150 tokens.  A state that is lost, zeroed or taken from another slot on the way shows at once."""
+    rt = Runtime(torch.device("cuda"), dtype)
+    hidden, heads, dk, dv = 48, 2, 16, 16
+    if kind == "retention":
+        m = {"heads": heads, "dim": dk, "vdim": dv, "decay": [1.0, 0.9995], "rot": {"dims": 8, "base": 40.0}}
+        mixer = build_part("mixer", PartSpec("retention", {"hidden": hidden, "n_heads": heads, "key_dim": dk, "value_dim": dv,
+                                                           "decay": (1.0, 0.9995), "eps": 1e-5,
+                                                           "position": PartSpec("rope", {"theta": 40.0, "dims": 8})}), rt)
+        w = fill(mixer, 21, 0.3)
+        fn = lambda wd: (lambda h, pos: plain.mixer_retention(h, wd, "p", m, 1e-5, pos))     # noqa: E731
+    elif kind == "wkv":
+        m = {"heads": heads, "dim": dk}
+        mixer = build_part("mixer", PartSpec("wkv", {"hidden": hidden, "n_heads": heads, "head_dim": dk, "decay_rank": 8, "eps": 1e-5}), rt)
+        w = fill(mixer, 22, 0.3)
+        w["w0"] = torch.full_like(w["w0"], -7.0)            # decays of exp(-exp(-7 + small)): about 0.999 per token
+        mixer.w_0.copy_(w["w0"])
+        fn = lambda wd: (lambda h, pos: plain.mixer_wkv(h, wd, "p", m, 1e-5))     # noqa: E731
+    else:
+        m = {"heads": heads, "dim": dk, "vdim": dv, "gate_cap": 10.0}
+        mixer = build_part("mixer", PartSpec("mlstm", {"hidden": hidden, "n_heads": heads, "key_dim": dk, "value_dim": dv,
+                                                       "gate_cap": 10.0, "eps": 1e-5}), rt)
+        w = fill(mixer, 23, 0.3)
+        w["f.b"] = torch.full_like(w["f.b"], 8.0)           # forget gates of about 1 - e^-8
+        mixer.b_gates[heads:].copy_(w["f.b"])
+        fn = lambda wd: (lambda h, pos: plain.mixer_mlstm(h, wd, "p", m, 1e-5))     # noqa: E731
+    wd = {k: v.double() for k, v in named(w).items()}
+    run_state_mixer(rt, mixer, hidden, fn(wd), loud_row=loud_row)
+
+
 WINDOW_SHAPES = [  # hidden, heads, kv heads, key size, value size, rotated dims, page, window
-    (48, 4, 2, 16, 32, 8, 8, 9), (40, 3, 1, 24, 24, 0, 4, 5), (36, 5, 5, 12, 20, 12, 2, 3), (64, 4, 2, 48, 96, 48, 16, 136),
+    (48, 4, 2, 16, 32, 8, 8, 9), (40, 3, 1, 24, 24, 0, 4, 5), (36, 5, 5, 12, 20, 12, 2, 3), (64, 6, 3, 40, 72, 20, 16, 100),
     (128, 8, 2, 64, 64, 64, 16, 40), (128, 4, 4, 32, 32, 16, 16, None), (64, 2, 1, 16, 16, 16, 8, 17), (64, 4, 2, 32, 16, 32, 8, 33),
 ]
 
@@ -260,7 +301,7 @@ def test_one_key_at_the_window_edge(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden,experts,top,ff,shared", [(64, 6, 2, 40, 24), (40, 3, 1, 20, None), (36, 5, 5, 9, 27), (128, 12, 4, 96, 128)])
+@pytest.mark.parametrize("hidden,experts,top,ff,shared", [(64, 6, 2, 40, 24), (40, 3, 1, 20, None), (36, 5, 5, 9, 27), (128, 10, 3, 88, 104)])
 def test_routed_experts_alone(dtype, hidden, experts, top, ff, shared):
     """Router logits that stand apart (no close calls), the softmax over the chosen logits alone, the weighted sum,
     the shared expert behind its own gate."""

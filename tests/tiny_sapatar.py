@@ -59,7 +59,7 @@ SAPATAR_C = {
     "architecture": "Sapatar", "vocab": 211, "width": 128, "norm": {"eps": 1e-6}, "streams": 1,
     "layers": [_C_PAR, retention(4, 32, 16, [0.5, 0.9, 0.99, 1.0], 8, 7e3),
                parallel(left(4, 4, 32, 32, None, 16, 2e4, 0.2), right(4, 16, 16, 8.0), 0.5, 0.5),
-               wkv(2, 64, 16, mlp=moe(4, 2, 32)), {**_C_PAR, "weights_of": 0}],
+               wkv(2, 64, 24, mlp=moe(4, 2, 32)), {**_C_PAR, "weights_of": 0}],
 }
 
 # sizes no fast path takes: a width that is no multiple of 8, odd head and feed-forward sizes, an odd vocabulary
