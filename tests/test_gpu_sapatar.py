@@ -9,7 +9,8 @@ import plain_sapatar as plain
 from helpers import (max_live_tokens, random_tokens, replay_in_process, schedule_mixed, schedule_portions, schedule_tail,
                      schedule_whole)
 from test_gpu_linurax import close, ctx_of, fill
-from tiny_sapatar import SAPATAR_CONFIGS, SAPATAR_PAGE, SAPATAR_SEEDS, SAPATAR_STD, left, moe, parallel, retention, right, wkv
+from tiny_sapatar import (SAPATAR_CONFIGS, SAPATAR_E, SAPATAR_PAGE, SAPATAR_SEEDS, SAPATAR_STD, left, moe, parallel, retention,
+                          right, wkv)
 
 import tessweave_engine_b200 as tw
 from tessweave_engine_b200.csrc import ops
@@ -513,6 +514,30 @@ def test_long_decoding_past_windows_and_pages(dtype, folders, tmp_path):
     want = plain.logits_of(folders[name, dtype], toks).numpy()
     low = plain.logits_of(folders[name, dtype], toks, torch.float32).numpy()
     compare(rows, {"long": want}, dtype, "long decoding", {"long": [row_error(low[p], want[p]) for p in range(len(toks))]})
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_of_hundreds_of_tokens_past_windows_of_tensor_core_sizes(dtype, tmp_path):
+    """Keys and values of one size (64, 32), windows of 70 and 150, prompts of 420 and 190 tokens: whole, with the last
+    40 tokens one by one, and in mixed batches, on pages of 16 that the windows give back on the way."""
+    cfg = SAPATAR_E if dtype == "float32" else {**SAPATAR_E, "norm": {"eps": 0.05}}
+    folder = tw.write_random_model(tmp_path / "model", cfg, seed=31, std=0.1)
+    if dtype == "bfloat16":
+        settle_router(folder)
+    reqs = {"long": random_tokens(cfg["vocab"], 420, 5), "mid": random_tokens(cfg["vocab"], 190, 6), "short": random_tokens(cfg["vocab"], 37, 7)}
+    want = {rid: plain.logits_of(folder, t).numpy() for rid, t in reqs.items()}
+    if dtype == "float32":
+        noise = {rid: [row_error(r, w) for r, w in zip(plain.logits_of(folder, t, torch.float32).numpy(), want[rid])] for rid, t in reqs.items()}
+    else:
+        config, weights = plain.read_folder(folder, torch.float64)
+        g = torch.Generator().manual_seed(98)
+        moved = {k: v * (1 + 2.0 ** -8 * torch.randn(v.shape, generator=g, dtype=torch.float64)) if v.dim() == 2 else v
+                 for k, v in weights.items()}
+        noise = {rid: [row_error(r, w) for r, w in zip(plain.forward(config, moved, t).float().numpy(), want[rid])] for rid, t in reqs.items()}
+    for kind, steps in (("whole", schedule_whole(reqs)), ("tail", schedule_tail(reqs, tail=40)),
+                        ("mixed", schedule_mixed(reqs, live=3, seed=2, prefill=(33, 2, 70, 5, 128, 16)))):
+        rows = replay_in_process(folder, dtype, steps, tmp_path / kind, block_size=16, max_tokens=max_live_tokens(steps))
+        compare(rows, want, dtype, f"E {kind}", noise)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -70,6 +70,15 @@ SAPATAR_D = {
                wkv(3, 12, 5, mlp=moe(2, 2, 9))],
 }
 
+# equal key and value sizes of 64 and 32 with windows that prompts of hundreds of tokens pass many times (the
+# tensor-core prompt kernel, and the decode kernel that is fed by TMA, with pages given back on the way)
+SAPATAR_E = {
+    "architecture": "Sapatar", "vocab": 300, "width": 96, "norm": {"eps": 1e-6}, "streams": 2,
+    "layers": [parallel(left(4, 2, 64, 64, 70, 32, 1e4, 0.125), right(2, 32, 32, 8.0), 1.1, 0.9, mlp=moe(6, 2, 32, shared=48)),
+               wkv(3, 32, 8),
+               parallel(left(2, 1, 32, 32, 150, 32, 5e5, 0.18), right(3, 16, 48, 5.0), 0.8, 1.2)],
+}
+
 SAPATAR_CONFIGS = {"A": SAPATAR_A, "B": SAPATAR_B, "C": SAPATAR_C, "D": SAPATAR_D}
 SAPATAR_PAGE = {"A": 8, "B": 4, "C": 16, "D": 2}
 SAPATAR_SEEDS = {"A": 15, "B": 16, "C": 17, "D": 18}
