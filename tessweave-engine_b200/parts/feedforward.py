@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, PartSpec, Runtime, StepContext, WeightDecl, build_part, dense_delta, join_name, register_part
-from .linear import grouped_matmul_nt, linear
+from .linear import grouped_matmul_nt, grouped_product_on_device, linear
 
 
 @register_part("feed_forward", "swiglu")
@@ -167,7 +167,8 @@ class RoutedExperts(FeedForward):
         # both ways' buffers are asked for in every step, so that the workspace has its final size after the largest one
         act = ws.get("moe.act", (n, self.top, self.intermediate), dt)
         sorted_buffers = self._sorted_buffers(ctx)
-        if self.grouped_for(n):
+        if self.grouped_for(n) and (grouped_product_on_device() or not ctx.fixed_shape):
+            # (a library without a grouped product reads the group bounds on the host: not inside a captured step)
             self._grouped(ctx, h, chosen, weight, shared, gate, out, sorted_buffers)
             return out
         ops.moe_gate_up(act, h, self.w_gate_up, chosen, n)

@@ -109,6 +109,12 @@ def linear(ctx, name: str, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dt
 _grouped_library: list = [None]     # True / False once the library's grouped product has been tried
 
 
+def grouped_product_on_device() -> bool:
+    """Whether ``grouped_matmul_nt`` runs without reading the group bounds on the host (so that it may stand inside a
+    captured CUDA graph)."""
+    return hasattr(torch, "_grouped_mm") and _grouped_library[0] is not False
+
+
 def grouped_matmul_nt(x: torch.Tensor, w: torch.Tensor, ends: torch.Tensor) -> torch.Tensor:
     """Rows of ``x`` in groups that stand together (group e = rows ends[e - 1] .. ends[e] - 1, ``ends`` int32 on the
     device), each group times its own matrix: out[i] = x[i] @ w[e(i)].T with ``w`` [groups, out, in].  bfloat16
