@@ -59,13 +59,13 @@ def test_decay_rank_comes_from_the_checkpoint(tmp_path):
     cfg = copy.deepcopy(SAPATAR_CONFIGS["B"])
     folder = tw.write_random_model(tmp_path / "m", cfg, seed=1)
     written = json.loads((folder / "config.json").read_text())
-    del written["layers"][1]["mixer"]["decay_rank"]
+    del written["layers"][2]["mixer"]["decay_rank"]
     (folder / "config.json").write_text(json.dumps(written))
     typed, _ = resolve_folder(folder)
-    assert typed.layers[1].mixer.decay_rank == 4
+    assert typed.layers[2].mixer.decay_rank == 4
     with pytest.raises(ValueError):
         resolve(written)                                     # neither the key nor a checkpoint
-    written["layers"][1]["mixer"]["decay_rank"] = 7
+    written["layers"][2]["mixer"]["decay_rank"] = 7
     (folder / "config.json").write_text(json.dumps(written))
     with pytest.raises(ConfigError):
         resolve_folder(folder)

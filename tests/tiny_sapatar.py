@@ -49,7 +49,7 @@ SAPATAR_A = {
 SAPATAR_B = {
     "architecture": "Sapatar", "vocab": 97, "width": 40, "norm": {"eps": 1e-6},
     "layers": [parallel(left(3, 1, 24, 24, 5, 0, 10.0, 0.25), right(1, 8, 40, 3.0), 1.0, 1.0, mlp=moe(3, 1, 20, shared=12)),
-               wkv(5, 8, 4), retention(1, 24, 40, [0.97], 12, 100.0, mlp=moe(5, 2, 16))],
+               retention(1, 24, 40, [0.97], 12, 100.0, mlp=moe(5, 2, 16)), wkv(5, 8, 4)],      # the last layer has no feed-forward
 }
 
 # sizes the tensor-core attention kernels take (key = value = 64, the whole head rotated, a window longer than a page;
