@@ -51,18 +51,19 @@ __device__ __forceinline__ float tw_dot_row8(const __nv_bfloat16* __restrict__ w
 
 // two rows of equal length at once (an expert's gate row and its up row): eight loads of a lane under way
 __device__ __forceinline__ void tw_dot2_row8(const __nv_bfloat16* __restrict__ wa, const __nv_bfloat16* __restrict__ wb,
-                                             const float* __restrict__ x, int n, int lane, float& da, float& db) {
+                                             const float* __restrict__ x, const float* __restrict__ y, int n, int lane,
+                                             float& da, float& db) {
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
     int i = lane * 8;
     for (; i + 768 < n; i += 1024) {
         const uint4 r0 = tw_stream16(wa + i), r1 = tw_stream16(wa + i + 256), r2 = tw_stream16(wa + i + 512), r3 = tw_stream16(wa + i + 768);
         const uint4 s0 = tw_stream16(wb + i), s1 = tw_stream16(wb + i + 256), s2 = tw_stream16(wb + i + 512), s3 = tw_stream16(wb + i + 768);
         a0 = tw_fma8(r0, x + i, a0); a1 = tw_fma8(r1, x + i + 256, a1); a2 = tw_fma8(r2, x + i + 512, a2); a3 = tw_fma8(r3, x + i + 768, a3);
-        b0 = tw_fma8(s0, x + i, b0); b1 = tw_fma8(s1, x + i + 256, b1); b2 = tw_fma8(s2, x + i + 512, b2); b3 = tw_fma8(s3, x + i + 768, b3);
+        b0 = tw_fma8(s0, y + i, b0); b1 = tw_fma8(s1, y + i + 256, b1); b2 = tw_fma8(s2, y + i + 512, b2); b3 = tw_fma8(s3, y + i + 768, b3);
     }
     for (; i < n; i += 256) {
         a0 = tw_fma8(tw_stream16(wa + i), x + i, a0);
-        b0 = tw_fma8(tw_stream16(wb + i), x + i, b0);
+        b0 = tw_fma8(tw_stream16(wb + i), y + i, b0);
     }
     da = tw_warp_sum((a0 + a1) + (a2 + a3));
     db = tw_warp_sum((b0 + b1) + (b2 + b3));
@@ -76,18 +77,19 @@ template <> __device__ __forceinline__ float tw_dot<__nv_bfloat16>(const __nv_bf
     return vec ? tw_dot_row8(w, x, n, lane) : tw_dot_row(w, x, n, lane);
 }
 
-template <typename T> __device__ __forceinline__ void tw_dot2(const T* wa, const T* wb, const float* x, int n, int lane, bool vec,
-                                                              float& da, float& db);
-template <> __device__ __forceinline__ void tw_dot2<float>(const float* wa, const float* wb, const float* x, int n, int lane, bool,
-                                                           float& da, float& db) {
+// da = wa . x and db = wb . y, the two rows streamed side by side
+template <typename T> __device__ __forceinline__ void tw_dot2(const T* wa, const T* wb, const float* x, const float* y, int n, int lane,
+                                                              bool vec, float& da, float& db);
+template <> __device__ __forceinline__ void tw_dot2<float>(const float* wa, const float* wb, const float* x, const float* y, int n,
+                                                           int lane, bool, float& da, float& db) {
     da = tw_dot_row(wa, x, n, lane);
-    db = tw_dot_row(wb, x, n, lane);
+    db = tw_dot_row(wb, y, n, lane);
 }
 template <> __device__ __forceinline__ void tw_dot2<__nv_bfloat16>(const __nv_bfloat16* wa, const __nv_bfloat16* wb, const float* x,
-                                                                   int n, int lane, bool vec, float& da, float& db) {
-    if (vec) { tw_dot2_row8(wa, wb, x, n, lane, da, db); return; }
+                                                                   const float* y, int n, int lane, bool vec, float& da, float& db) {
+    if (vec) { tw_dot2_row8(wa, wb, x, y, n, lane, da, db); return; }
     da = tw_dot_row(wa, x, n, lane);
-    db = tw_dot_row(wb, x, n, lane);
+    db = tw_dot_row(wb, y, n, lane);
 }
 
 template <typename T>
@@ -168,7 +170,7 @@ moe_gate_up_kernel(T* __restrict__ act, const T* __restrict__ h, int h_stride, c
     const int f0 = blockIdx.y * rows_per_block, f1 = min(F, f0 + rows_per_block);
     for (int f = f0 + warp; f < f1; f += TW_MOE_WARPS) {
         float g, u;
-        tw_dot2<T>(wg + (size_t)f * width, wu + (size_t)f * width, sm, width, lane, vec, g, u);
+        tw_dot2<T>(wg + (size_t)f * width, wu + (size_t)f * width, sm, sm, width, lane, vec, g, u);
         if (lane == 0) act[(size_t)pair * F + f] = tw_from_float<T>(g / (1.0f + expf(-g)) * u);
     }
 }
@@ -207,7 +209,17 @@ moe_down_kernel(T* __restrict__ out, const T* __restrict__ act, const T* __restr
     const int c0 = blockIdx.y * cols_per_block, c1 = min(width, c0 + cols_per_block);
     for (int c = c0 + warp; c < c1; c += TW_MOE_WARPS) {
         float acc = 0.f;
-        for (int j = 0; j < top; ++j) {
+        int j = 0;
+        for (; j + 1 < top; j += 2) {            // two experts' rows side by side; always added in the order of the experts
+            const int e0 = chosen[(size_t)row * top + j], e1 = chosen[(size_t)row * top + j + 1];
+            if (e0 < 0 || e0 >= E || e1 < 0 || e1 >= E) continue;
+            float d0, d1;
+            tw_dot2<T>(wd + ((size_t)e0 * width + c) * F, wd + ((size_t)e1 * width + c) * F, sm + (size_t)j * F, sm + (size_t)(j + 1) * F,
+                       F, lane, vec, d0, d1);
+            acc += weight[(size_t)row * top + j] * d0;
+            acc += weight[(size_t)row * top + j + 1] * d1;
+        }
+        for (; j < top; ++j) {
             const int e = chosen[(size_t)row * top + j];
             if (e < 0 || e >= E) continue;
             acc += weight[(size_t)row * top + j] * tw_dot<T>(wd + ((size_t)e * width + c) * F, sm + (size_t)j * F, F, lane, vec);
@@ -226,7 +238,7 @@ TW_EXPORT int tw_moe_down(void* out, const void* act, const void* wd, const int*
     const size_t smem = (size_t)top * F * sizeof(float);
     if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
     int per = width;
-    while (per > 4 * TW_MOE_WARPS && (size_t)rows * ((width + per - 1) / per) < 592) per = (per + 1) / 2;
+    while (per > TW_MOE_WARPS && (size_t)rows * ((width + per - 1) / per) < 592) per = (per + 1) / 2;
     per = ((per + TW_MOE_WARPS - 1) / TW_MOE_WARPS) * TW_MOE_WARPS;
     const dim3 grid(rows, (width + per - 1) / per);
     if (dtype == TW_F32) {

@@ -97,13 +97,13 @@ class RoutedExperts(FeedForward):
     [1, hidden]).  Expert e's matrices are ``<expert_prefix><e>.gate|up|down`` in the checkpoint and live stacked:
     gate and up as [experts, 2, ff, hidden], down as [experts, hidden, ff].  The weighted sum is fp32.
 
-    bfloat16 steps (with more than ``GROUPED_MIN_ROWS`` rows, and matrices whose rows start on 16-byte boundaries) sort
+    bfloat16 steps with more than ``GROUPED_MIN_ROWS`` rows (and matrices whose rows start on 16-byte boundaries) sort
     the pairs by expert and run every expert's rows through one library product, whose group bounds stay on the device.
-    float32 steps and odd sizes run each (token, expert) pair as matrix-vector products that stream the chosen
-    experts' matrices (csrc/moe.cu).
+    Steps of one row, float32 steps and odd sizes run each (token, expert) pair as matrix-vector products that stream
+    the chosen experts' matrices (csrc/moe.cu).
     """
 
-    GROUPED_MIN_ROWS = 0       # measured at 7B and 1.5B layer sizes: the sorted way is the faster one from one row on
+    GROUPED_MIN_ROWS = 1       # measured at 7B and 1.5B layer sizes: the sorted way is the faster one from two or three rows on
 
     def __init__(self, runtime: Runtime, hidden: int, experts: int, top: int, intermediate: int,
                  shared: PartSpec | None = None, shared_gate: bool = False, router_bias: bool = True,
